@@ -28,7 +28,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
-from ..config.spec import FixedState, PagedKv
+from ..config.spec import FixedState, PagedKv, split_requirement
 from ..errors import KvCachePressure, KvCapacity, NoFreeSlot
 from .pages import PagePool
 from .prefix import PrefixIndex, page_key
@@ -47,6 +47,11 @@ class GroupInfo:
     def window(self) -> Optional[int]:
         return self.requirement.window
 
+    @property
+    def keep_first(self) -> int:
+        """With a window: the request's first tokens that every later query still sees (their pages stay)."""
+        return self.requirement.keep_first if self.requirement.window is not None else 0
+
 
 @dataclass
 class Sequence_:
@@ -62,6 +67,7 @@ class Sequence_:
     tokens: Optional[List[int]] = None                # with a prefix cache: the ids of the cached tokens (None: unknown)
     keys: List[bytes] = field(default_factory=list)   # with a prefix cache: the key of every full page so far
     prefix_tokens: int = 0                            # tokens this request found cached when it was admitted
+    last_token: int = -1                              # the id fed last (-1: none yet), for embeddings of token pairs
 
 
 class CacheManager:
@@ -78,23 +84,24 @@ class CacheManager:
         self.groups: List[GroupInfo] = []
         self.entry_group: Dict[int, int] = {}          # schedule entry -> group (paged entries)
         self.entry_local: Dict[int, int] = {}          # schedule entry -> index of its storage within the group
-        self.state_entries: Dict[int, FixedState] = {} # schedule entry -> fixed state it owns
+        # schedule entry -> the fixed state it owns (a tuple of them where a mixer of several mechanisms asked for more)
+        self.state_entries: Dict[int, object] = {}
         by_requirement: Dict[PagedKv, GroupInfo] = {}
         for item in plan:
-            if isinstance(item.requirement, PagedKv):
-                if item.source == item.entry:
-                    group = by_requirement.get(item.requirement)
-                    if group is None:
-                        group = GroupInfo(len(self.groups), item.requirement, [], PagePool(num_pages))
-                        by_requirement[item.requirement] = group
-                        self.groups.append(group)
-                    self.entry_local[item.entry] = len(group.entries)
-                    group.entries.append(item.entry)
-                    self.entry_group[item.entry] = group.index
-            elif isinstance(item.requirement, FixedState) and item.source == item.entry:
-                self.state_entries[item.entry] = item.requirement
+            paged, states = split_requirement(item.requirement)
+            if paged is not None and item.source == item.entry:
+                group = by_requirement.get(paged)
+                if group is None:
+                    group = GroupInfo(len(self.groups), paged, [], PagePool(num_pages))
+                    by_requirement[paged] = group
+                    self.groups.append(group)
+                self.entry_local[item.entry] = len(group.entries)
+                group.entries.append(item.entry)
+                self.entry_group[item.entry] = group.index
+            if states and item.source == item.entry:
+                self.state_entries[item.entry] = states[0] if len(states) == 1 else states
         for item in plan:                              # readers of another entry's cache
-            if item.source != item.entry and isinstance(item.requirement, PagedKv):
+            if item.source != item.entry and split_requirement(item.requirement)[0] is not None:
                 self.entry_group[item.entry] = self.entry_group[item.source]
                 self.entry_local[item.entry] = self.entry_local[item.source]
         capable = len(self.groups) == 1 and self.groups[0].window is None and not self.state_entries
@@ -160,7 +167,8 @@ class CacheManager:
         if group.window is None:
             return self._blocks_for(length)
         span = min(length, group.window + portion)
-        return min(self._blocks_for(length), span // self.page_size + 2)
+        kept = self._blocks_for(min(length, group.keep_first))
+        return min(self._blocks_for(length), span // self.page_size + 2 + kept)
 
     def can_grow(self, sequence: Sequence_, new_length: int, spare: Optional[List[int]] = None) -> bool:
         need = self.pages_needed(sequence, new_length)
@@ -175,7 +183,8 @@ class CacheManager:
         for n, group, table, first in zip(need, self.groups, sequence.tables, sequence.first_live):
             if n == 0:
                 continue
-            live_now = len(table) - first                    # the blocks before `first` were given back
+            # the blocks before `first` were given back, but for those of the first tokens a window keeps
+            live_now = len(table) - max(0, first - self._blocks_for(group.keep_first))
             if live_now + n > group.pool.count:
                 raise KvCapacity(live_now + n, group.pool.count, f"group {group.index}")
             if n > group.pool.available:
@@ -236,12 +245,17 @@ class CacheManager:
             dead_keys = new_length - group.window + 1       # keys < dead_keys are never read again
             dead_blocks = max(0, dead_keys // self.page_size)
             table = sequence.tables[index]
-            first = sequence.first_live[index]
+            # blocks that hold one of the first `keep_first` tokens are never given back
+            first = max(sequence.first_live[index], self._blocks_for(group.keep_first))
             if dead_blocks > first:
                 group.pool.give_back(page for page in table[first:dead_blocks] if page >= 0)
                 for block in range(first, dead_blocks):
                     table[block] = -1
                 sequence.first_live[index] = dead_blocks
+        if tokens is not None and len(tokens) > 0:
+            sequence.last_token = int(tokens[-1])
+        else:
+            sequence.last_token = -2                        # unknown: the ids stayed on the device
 
     def release(self, request_id) -> None:
         """Give back every page and the slot of a request."""

@@ -9,8 +9,8 @@ Per schedule entry with fixed-size state: [max_requests, *shape], one record per
 
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Dict, Optional
+from dataclasses import dataclass, replace
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -28,7 +28,16 @@ class CacheView:
     v_pages: Optional[torch.Tensor] = None
     page_size: int = 0
     writes: bool = True                     # False: the entry reads another entry's cache
-    state: Optional[torch.Tensor] = None    # [max_requests, *shape] fixed-size state, indexed by slot
+    state: Optional[torch.Tensor] = None    # [max_requests, *shape] fixed-size state, indexed by slot (the first one)
+    states: Tuple[torch.Tensor, ...] = ()   # every fixed-size state of the entry, in the order they were asked for
+
+    def part(self, pages: bool, first_state: int, state_count: int) -> "CacheView":
+        """What one mechanism of a mixer made of several sees: the pages (or none) and its own run of the states."""
+        mine = tuple(self.states[first_state:first_state + state_count])
+        view = replace(self, states=mine, state=mine[0] if mine else None)
+        if not pages:
+            view.group, view.k_pages, view.v_pages = None, None, None
+        return view
 
 
 class CacheStorage:
@@ -43,10 +52,11 @@ class CacheStorage:
             self.value_buffers.append(torch.zeros((len(group.entries), rows, r.kv_heads, r.value_dim), dtype=dtype,
                                                   device=device))
         self.buffers = self.key_buffers + self.value_buffers
-        self.states: Dict[int, torch.Tensor] = {}
+        self.states: Dict[int, object] = {}        # entry -> tensor, or tuple of tensors where the entry has several
+        make = lambda requirement: torch.zeros((manager.max_requests, *requirement.shape),
+                                               dtype=_DTYPES[requirement.dtype], device=device)
         for entry, requirement in manager.state_entries.items():
-            self.states[entry] = torch.zeros((manager.max_requests, *requirement.shape),
-                                             dtype=_DTYPES[requirement.dtype], device=device)
+            self.states[entry] = tuple(make(r) for r in requirement) if isinstance(requirement, tuple) else make(requirement)
         self.views: Dict[int, CacheView] = {}
         for item in plan:
             view = CacheView(writes=item.source == item.entry)
@@ -58,17 +68,21 @@ class CacheStorage:
                 view.v_pages = self.value_buffers[group][local]
                 view.page_size = manager.page_size
             if item.source in self.states:
-                view.state = self.states[item.source]
+                held = self.states[item.source]
+                view.states = held if isinstance(held, tuple) else (held,)
+                view.state = view.states[0]
             self.views[item.entry] = view
 
     def zero_slots(self, slots) -> None:
         """Fixed-size state of newly admitted requests starts at zero."""
         if not slots or not self.states:
             return
-        index = torch.tensor(slots, dtype=torch.long, device=next(iter(self.states.values())).device)
-        for state in self.states.values():
+        tensors = [t for held in self.states.values() for t in (held if isinstance(held, tuple) else (held,))]
+        index = torch.tensor(slots, dtype=torch.long, device=tensors[0].device)
+        for state in tensors:
             state.index_fill_(0, index, 0)
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self.buffers) + \
-            sum(s.numel() * s.element_size() for s in self.states.values())
+            sum(t.numel() * t.element_size() for held in self.states.values()
+                for t in (held if isinstance(held, tuple) else (held,)))

@@ -63,6 +63,7 @@ class PagedKv:
     head_dim: int
     window: Optional[int] = None
     value_head_dim: Optional[int] = None
+    keep_first: int = 0           # with a window: the request's first tokens whose pages are never given back
 
     @property
     def value_dim(self) -> int:
@@ -82,7 +83,48 @@ class FixedState:
     dtype: str = "float32"
 
 
-CacheRequirement = Union[PagedKv, FixedState, None]
+@dataclass(frozen=True)
+class CacheBundle:
+    """What a mixer made of several mechanisms asks for one schedule entry: at most one set of pages and any number
+    of fixed-size states, in the order its parts will find them in CacheView.states."""
+
+    paged: Optional[PagedKv] = None
+    states: tuple = ()
+
+
+CacheRequirement = Union[PagedKv, FixedState, CacheBundle, None]
+
+
+def split_requirement(requirement) -> tuple:
+    """(PagedKv or None, tuple of FixedState) of any cache requirement."""
+    if requirement is None:
+        return None, ()
+    if isinstance(requirement, PagedKv):
+        return requirement, ()
+    if isinstance(requirement, FixedState):
+        return None, (requirement,)
+    if isinstance(requirement, CacheBundle):
+        return requirement.paged, tuple(requirement.states)
+    raise ConfigError(f"unknown cache requirement {requirement!r}")
+
+
+def bundle_requirements(requirements) -> CacheRequirement:
+    """One requirement for several parts that share a schedule entry (None if none of them asks for anything)."""
+    paged, states = None, []
+    for requirement in requirements:
+        pages, fixed = split_requirement(requirement)
+        if pages is not None:
+            if paged is not None:
+                raise ConfigError("one schedule entry holds at most one set of cache pages")
+            paged = pages
+        states.extend(fixed)
+    if paged is None and not states:
+        return None
+    if paged is not None and not states:
+        return paged
+    if paged is None and len(states) == 1:
+        return states[0]
+    return CacheBundle(paged, tuple(states))
 
 
 # --------------------------------------------------------------------------- parts
@@ -95,8 +137,13 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class RmsNormSpec(PartSpec):
+    """y = x / sqrt(mean(x^2) + eps) * (offset + w).  `offset` 1 is the form whose weight is stored around zero;
+    `tensor` is the local name of the weight ("" where the checkpoint names the norm itself)."""
+
     size: int = 0
     eps: float = 1e-5
+    offset: float = 0.0
+    tensor: str = "weight"
     kind: str = field(init=False, default="rms_norm")
 
 
@@ -124,7 +171,14 @@ class SoftmaxAttentionSpec(PartSpec):
     out_bias: bool = False
     window: Optional[int] = None
     position: Optional[PartSpec] = None
+    value_head_dim: Optional[int] = None     # width of a value head where it differs from head_dim
+    keep_first: int = 0                      # with a window: the first tokens every later query still sees
+    names: tuple = ()                        # (local name, stored name) pairs for checkpoints with names of their own
     kind: str = field(init=False, default="softmax_attention")
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.value_head_dim is None else self.value_head_dim
 
 
 @dataclass(frozen=True)
@@ -134,6 +188,59 @@ class SwiGluSpec(PartSpec):
     kind: str = field(init=False, default="swiglu")
 
 
+@dataclass(frozen=True)
+class GeluMlpSpec(PartSpec):
+    """down(gelu_tanh(up(x))): a dense feed-forward without a gate."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    kind: str = field(init=False, default="gelu_mlp")
+
+
+@dataclass(frozen=True)
+class GatedDeltaRuleSpec(PartSpec):
+    """The gated delta rule (parts/delta_rule.py).  `decay`: "head" one decay per head from a full projection `a`,
+    "channel" one per head and key channel from a low-rank pair `a1`, `a2` of rank `decay_rank`.  `gate`: "silu" of
+    a full projection `g`, or "sigmoid" of a low-rank pair `g1`, `g2` of rank `gate_rank`."""
+
+    hidden_size: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 4
+    decay: str = "head"
+    decay_rank: int = 0
+    gate: str = "silu"
+    gate_rank: int = 0
+    norm_eps: float = 1e-5
+    kind: str = field(init=False, default="gated_delta_rule")
+
+
+@dataclass(frozen=True)
+class SideBySideSpec(PartSpec):
+    """Several mixers that read the same input; the result is `scale` times the sum of their outputs, each first
+    RMS-normed over the model width with a plain weight `<branch name>.<out_tensor>`."""
+
+    hidden_size: int = 0
+    branches: tuple = ()                     # (name, PartSpec) pairs; a branch's tensors lie under "<name>."
+    eps: float = 1e-5
+    scale: float = 0.5
+    out_tensor: str = "out"
+    kind: str = field(init=False, default="side_by_side")
+
+
+@dataclass(frozen=True)
+class TokenPairsSpec:
+    """A second embedding table added to the first, indexed by a hash of a token and the one before it:
+    row (previous * mul_previous + token * mul_current) mod buckets; a request's first token takes row `buckets`."""
+
+    name: str
+    buckets: int
+    mul_previous: int
+    mul_current: int
+
+
 # --------------------------------------------------------------------------- layers and model
 @dataclass(frozen=True)
 class LayerSpec:
@@ -141,6 +248,8 @@ class LayerSpec:
 
     `prefix` is the checkpoint prefix of the layer; `names` maps each slot of the
     arrangement to the sub-prefix of its tensors, so names are data of the architecture.
+    Arrangements: "pre_norm" (a norm before each of the two branches, one after the other) and "parallel" (one
+    norm, `mixer_norm`, whose output both branches read; `feed_forward_norm` is None).
     """
 
     prefix: str
@@ -170,16 +279,19 @@ class EmbeddingSpec:
     vocab_size: int
     hidden_size: int
     multiplier: float = 1.0
+    pairs: Optional[TokenPairsSpec] = None
 
 
 @dataclass(frozen=True)
 class HeadSpec:
-    """Output projection; `tied_to` names the embedding tensor it shares, else `name` is its own."""
+    """Output projection; `tied_to` names the embedding tensor it shares, else `name` is its own.  `scale`
+    multiplies the logits."""
 
     name: str
     vocab_size: int
     hidden_size: int
     tied: bool = False
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)

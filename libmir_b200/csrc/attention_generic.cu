@@ -11,7 +11,9 @@
 // Replaces libmir's paged_attention_bf16.cu:14-93, paged_attention_batch_bf16.cu:14-102 and
 // paged_prefill_attention_batch_bf16.cu:14-124: score = (q . k) * scale, running maximum and
 // denominator, all in 32-bit; key j is visible to the query at position p iff j <= p and
-// (window == 0 or j > p - window).
+// (window == 0 or j > p - window or j < keep_first): with a window, the first keep_first keys of a request stay
+// visible to every later query (they keep their pages and their true positions).  Values may be narrower or wider
+// than keys (value_dim).  A query walks over the kept keys first, then over its window.
 #include <cfloat>
 #include "common.cuh"
 
@@ -25,7 +27,7 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, size_t q_token_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ row_of_token, const int* __restrict__ positions, int page_size, int heads, int kv_heads,
-    int head_dim, float scale, int window) {
+    int head_dim, int value_dim, float scale, int window, int keep_first) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int lane = threadIdx.x;
   const int warp = threadIdx.y;
@@ -48,15 +50,22 @@ __global__ void paged_attention_generic_kernel(
   float running_max = -FLT_MAX;
   float denominator = 0.0f;
 
-  for (int base = first_key; base <= position; base += 32) {
+  // the kept first keys that lie before the window, then the window: [0, kept) and [first_key, position]
+  const int kept = min(keep_first, first_key);
+  const int kept_chunks = (kept + 31) / 32;
+  const int chunks = kept_chunks + (position - first_key) / 32 + 1;
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const bool in_kept = chunk < kept_chunks;
+    const int base = in_kept ? chunk * 32 : first_key + (chunk - kept_chunks) * 32;
+    const int last = in_kept ? kept - 1 : position;
     const int key = base + lane;
-    const bool valid = key <= position;
+    const bool valid = key <= last;
     float score = -FLT_MAX;
     size_t key_offset = 0;
     if (valid) {
       const int page = table[key / page_size];
-      key_offset = (((size_t)page * page_size + key % page_size) * kv_heads + kv_head) * head_dim;
-      const T* k_row = k_pages + key_offset;
+      key_offset = ((size_t)page * page_size + key % page_size) * kv_heads + kv_head;
+      const T* k_row = k_pages + key_offset * head_dim;
       float dot = 0.0f;
       for (int d = 0; d < head_dim; d += 8) {
         float k8[8];
@@ -72,26 +81,26 @@ __global__ void paged_attention_generic_kernel(
     denominator = denominator * correction + warp_sum(weight);
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= correction;
-    const int keys_here = min(32, position - base + 1);
+    const int keys_here = min(32, last - base + 1);
     for (int j = 0; j < keys_here; ++j) {
       const float w = __shfl_sync(0xffffffffu, weight, j);
       const size_t offset = __shfl_sync(0xffffffffu, key_offset, j);
-      const T* v_row = v_pages + offset;
+      const T* v_row = v_pages + offset * value_dim;
 #pragma unroll
       for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) acc[i] = fmaf(w, to_float(v_row[d]), acc[i]);
+        if (d < value_dim) acc[i] = fmaf(w, to_float(v_row[d]), acc[i]);
       }
     }
     running_max = next_max;
   }
 
-  T* out_row = out + ((size_t)token * heads + head) * head_dim;
+  T* out_row = out + ((size_t)token * heads + head) * value_dim;
   const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;   // a padded row has no keys
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < head_dim) out_row[d] = from_float<T>(acc[i] * inverse);
+    if (d < value_dim) out_row[d] = from_float<T>(acc[i] * inverse);
   }
 }
 
@@ -99,11 +108,11 @@ __global__ void paged_attention_generic_kernel(
 MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_token_stride, void* out,
                                            const void* k_pages, const void* v_pages, const int* block_table,
                                            int table_width, const int* row_of_token, const int* positions, int tokens,
-                                           int page_size, int heads, int kv_heads, int head_dim, float scale,
-                                           int window, cudaStream_t stream) {
+                                           int page_size, int heads, int kv_heads, int head_dim, int value_dim,
+                                           float scale, int window, int keep_first, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 ||
-      window < 0) {
+      window < 0 || keep_first < 0) {
     mir_set_error("paged_attention: bad sizes (tokens %d, heads %d, kv heads %d, page %d, table width %d)", tokens,
                   heads, kv_heads, page_size, table_width);
     return MIR_BAD_ARGUMENT;
@@ -112,16 +121,21 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
     mir_set_error("paged_attention: head_dim %d is not a multiple of 8 in [8, %d]", head_dim, kMaxHeadDim);
     return MIR_BAD_ARGUMENT;
   }
+  if (value_dim <= 0 || value_dim > kMaxHeadDim) {
+    mir_set_error("paged_attention: value_dim %d is not in [1, %d]", value_dim, kMaxHeadDim);
+    return MIR_BAD_ARGUMENT;
+  }
   const dim3 grid(tokens, (heads + kWarpsPerBlock - 1) / kWarpsPerBlock);
   const dim3 block(32, kWarpsPerBlock);
   if (bf16)
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const __nv_bfloat16*)q, (size_t)q_token_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pages,
         (const __nv_bfloat16*)v_pages, block_table, table_width, row_of_token, positions, page_size, heads, kv_heads,
-        head_dim, scale, window);
+        head_dim, value_dim, scale, window, keep_first);
   else
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const float*)q, (size_t)q_token_stride, (float*)out, (const float*)k_pages, (const float*)v_pages,
-        block_table, table_width, row_of_token, positions, page_size, heads, kv_heads, head_dim, scale, window);
+        block_table, table_width, row_of_token, positions, page_size, heads, kv_heads, head_dim, value_dim, scale,
+        window, keep_first);
   return mir_check_launch("paged_attention_generic");
 }

@@ -33,7 +33,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xc
 LIBRARIES = {
     "core": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
-                    "sampling.cu", "executor.cu"],
+                    "sampling.cu", "executor.cu", "delta_rule.cu"],
         "link": [],
         "defines": [],
     },
@@ -41,7 +41,7 @@ LIBRARIES = {
     "bf16": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
                     "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "attention_tc_decode.cu",
-                    "gemm_tc_stream.cu", "ops_bf16.cu", "executor.cu"],
+                    "gemm_tc_stream.cu", "ops_bf16.cu", "executor.cu", "delta_rule.cu"],
         "headers": ["no_alloc.h", "tcgen05.cuh"],
         "link": ["-lcublasLt"],
         "defines": ["-DMIR_WITH_BF16"],

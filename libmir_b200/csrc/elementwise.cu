@@ -23,6 +23,69 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(src[c]) * scale : 0.0f;
 }
 
+// out[r, :] = float(table[ids[r], :]) * scale + float(pairs[bucket(r), :]): a second table indexed by a hash of the
+// token and the token before it in its request, bucket = (previous * mul_previous + id * mul_current) mod buckets;
+// a request's first token (previous < 0) takes row `buckets`, the table's last.
+template <typename T>
+__global__ void embed_pairs_kernel(const T* __restrict__ table, const T* __restrict__ pairs, const int* __restrict__ ids,
+                                   const int* __restrict__ previous, float* __restrict__ out, int hidden, int vocab,
+                                   int buckets, long long mul_previous, long long mul_current, float scale) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const int before = previous[row];
+  const bool ok = id >= 0 && id < vocab;
+  const long long bucket = before < 0 ? (long long)buckets
+                                      : (((long long)before * mul_previous + (long long)id * mul_current) % buckets + buckets) % buckets;
+  const T* src = table + (size_t)(ok ? id : 0) * hidden;
+  const T* pair = pairs + (size_t)bucket * hidden;
+  float* dst = out + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    dst[c] = ok ? to_float(src[c]) * scale + to_float(pair[c]) : 0.0f;
+}
+
+// x <- 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), in place.
+template <typename T>
+__global__ void gelu_tanh_kernel(T* __restrict__ x, size_t total) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const float z = to_float(x[index]);
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  x[index] = from_float<T>(0.5f * z * (1.0f + tanhf(inner)));
+}
+
+// residual[r, :] += scale * sum over branches b of branch_b[r, :] * rsqrt(mean(branch_b[r, :]^2) + eps) * weight_b:
+// several branch outputs (32-bit rows), each normalised over the model width with a weight of its own, added to the
+// residual stream in one pass.  Fixed reduction tree per branch.
+struct NormedBranches {
+  const float* rows[4];
+  const float* weight[4];
+  int count;
+};
+__global__ void add_normed_branches_kernel(NormedBranches branches, float* __restrict__ residual, int hidden, float eps,
+                                           float scale) {
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  float inverse[4];
+  for (int b = 0; b < branches.count; ++b) {
+    const float* src = branches.rows[b] + (size_t)row * hidden;
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) sum = fmaf(src[c], src[c], sum);
+    sum = block_sum(sum, scratch);
+    inverse[b] = rsqrtf(sum / (float)hidden + eps);
+  }
+  float* dst = residual + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float total = 0.0f;
+    for (int b = 0; b < branches.count; ++b)
+      total += branches.rows[b][(size_t)row * hidden + c] * inverse[b] * branches.weight[b][c];
+    dst[c] += scale * total;
+  }
+}
+
 // y[r, :] = x[src(r), :] * rsqrt(mean(x^2) + eps) * w, src(r) = rows ? rows[r] : r.
 // Sum of squares and scaling in 32-bit with a fixed reduction tree.
 template <typename Tout>
@@ -145,6 +208,39 @@ MIR_EXPORT int mir_embed(int bf16, const void* table, const int* ids, float* out
                     hidden, vocab, scale);
 }
 
+MIR_EXPORT int mir_embed_pairs(int bf16, const void* table, const void* pairs, const int* ids, const int* previous,
+                               float* out, int rows, int hidden, int vocab, int buckets, long long mul_previous,
+                               long long mul_current, float scale, cudaStream_t stream) {
+  if (rows == 0) return MIR_OK;
+  if (rows < 0 || hidden <= 0 || vocab <= 0 || buckets <= 0) { mir_set_error("embed_pairs: bad sizes"); return MIR_BAD_ARGUMENT; }
+  if (bf16)
+    return mir_launch("embed_pairs", embed_pairs_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, 0,
+                      (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, ids, previous, out, hidden, vocab,
+                      buckets, mul_previous, mul_current, scale);
+  return mir_launch("embed_pairs", embed_pairs_kernel<float>, dim3(rows), dim3(256), 0, stream, 0, (const float*)table,
+                    (const float*)pairs, ids, previous, out, hidden, vocab, buckets, mul_previous, mul_current, scale);
+}
+
+MIR_EXPORT int mir_gelu_tanh(int bf16, void* x, size_t total, cudaStream_t stream) {
+  if (bf16) LAUNCH_1D(gelu_tanh_kernel, total, (__nv_bfloat16*)x, total);
+  else LAUNCH_1D(gelu_tanh_kernel, total, (float*)x, total);
+  return mir_check_launch("gelu_tanh");
+}
+
+// rows_b, weight_b: `count` (1 to 4) pointers each, to 32-bit [rows, hidden] and [hidden].
+MIR_EXPORT int mir_add_normed_branches(const float* const* branch_rows, const float* const* branch_weights, int count,
+                                       float* residual, int rows, int hidden, float eps, float scale,
+                                       cudaStream_t stream) {
+  if (rows == 0) return MIR_OK;
+  if (rows < 0 || hidden <= 0 || count < 1 || count > 4) { mir_set_error("add_normed_branches: bad sizes"); return MIR_BAD_ARGUMENT; }
+  NormedBranches branches = {};
+  branches.count = count;
+  for (int b = 0; b < count; ++b) { branches.rows[b] = branch_rows[b]; branches.weight[b] = branch_weights[b]; }
+  const int threads = hidden >= 2048 ? 512 : 256;
+  return mir_launch("add_normed_branches", add_normed_branches_kernel, dim3(rows), dim3(threads), 0, stream, 0, branches,
+                    residual, hidden, eps, scale);
+}
+
 MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void* out, const int* rows, int n_rows,
                             int hidden, float eps, cudaStream_t stream) {
   if (n_rows == 0) return MIR_OK;
@@ -243,13 +339,14 @@ __global__ void decode_prepare_kernel(const int* __restrict__ positions, const i
 // appended to a log so that several steps can run without the host reading each one.
 __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ tokens,
                                       int* __restrict__ positions, int* __restrict__ token_log, int log_steps,
-                                      int* __restrict__ step_counter, int rows) {
+                                      int* __restrict__ step_counter, int rows, int* __restrict__ previous) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int step = *step_counter;
   __syncthreads();
   for (int row = threadIdx.x; row < rows; row += blockDim.x) {
     const int token = sampled[row];
+    if (previous) previous[row] = tokens[row];      // the token before the next one, for models that look at pairs
     tokens[row] = token;
     if (positions[row] >= 0) positions[row] += 1;
     if (step < log_steps) token_log[(size_t)step * rows + row] = token;
@@ -265,8 +362,8 @@ MIR_EXPORT int mir_decode_prepare(const int* positions, const int* block_table, 
 }
 
 MIR_EXPORT int mir_decode_advance(const int* sampled, int* tokens, int* positions, int* token_log, int log_steps,
-                                  int* step_counter, int rows, cudaStream_t stream) {
+                                  int* step_counter, int rows, int* previous, cudaStream_t stream) {
   if (rows <= 0) return MIR_OK;
   return mir_launch("decode_advance", decode_advance_kernel, dim3(1), dim3(256), 0, stream, 0, sampled, tokens,
-                    positions, token_log, log_steps, step_counter, rows);
+                    positions, token_log, log_steps, step_counter, rows, previous);
 }

@@ -1,5 +1,6 @@
 // Per-head q/k RMSNorm, rotary position encoding and the write of K and V into cache pages, in one
-// kernel over the packed [T, (Hq + 2 Hkv) D] output of the QKV projection.
+// kernel over the packed [T, (Hq + Hkv) D + Hkv Dv] output of the QKV projection (Dv = D unless the values have a
+// width of their own).
 //
 // Replaces libmir's qkv_postprocess_bf16.cu:71-183 and kv_cache_bf16.cu:74-97 (two launches and a
 // round trip of k and v through memory).  Differences on purpose: the normalised value is not
@@ -35,7 +36,8 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq,
                                      const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads,
-                                     int head_dim, int rotary_dim, float eps, int write_kv, int units_per_cta) {
+                                     int head_dim, int value_dim, int rotary_dim, float eps, int write_kv,
+                                     int units_per_cta) {
   extern __shared__ float angles[];                 // [half] cosines then [half] sines of this token
   grid_launch_dependents();
   grid_dependency_wait();
@@ -43,7 +45,7 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int units = heads + 2 * kv_heads;
-  const size_t row_width = (size_t)units * head_dim;
+  const size_t row_width = (size_t)(heads + kv_heads) * head_dim + (size_t)kv_heads * value_dim;
   T* row = qkv + (size_t)token * row_width;
   const float position = (float)positions[token];
   const int slot = slot_mapping ? slot_mapping[token] : -1;
@@ -57,12 +59,14 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
     T* src = row + (size_t)unit * head_dim;
     if (unit >= heads + kv_heads) {                 // a value head: copy to its page
       if (write_kv != 1 || slot < 0) continue;
-      T* dst = v_pages + ((size_t)slot * kv_heads + (unit - heads - kv_heads)) * head_dim;
-      if ((head_dim * sizeof(T)) % 16 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0) {
-        const int chunks = head_dim * (int)sizeof(T) / 16;
+      const int value_head = unit - heads - kv_heads;
+      src = row + (size_t)(heads + kv_heads) * head_dim + (size_t)value_head * value_dim;
+      T* dst = v_pages + ((size_t)slot * kv_heads + value_head) * value_dim;
+      if ((value_dim * sizeof(T)) % 16 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0) {
+        const int chunks = value_dim * (int)sizeof(T) / 16;
         for (int c = lane; c < chunks; c += 32) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
       } else {
-        for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
+        for (int d = lane; d < value_dim; d += 32) dst[d] = src[d];
       }
       continue;
     }
@@ -239,7 +243,7 @@ int launch_rope_wide(__nv_bfloat16* qkv, const int* positions, const int* slot_m
 template <typename T>
 int launch_rope(T* qkv, const int* positions, const int* slot_mapping, const float* inv_freq, const float* q_norm,
                 const float* k_norm, T* k_pages, T* v_pages, int tokens, int heads, int kv_heads, int head_dim,
-                int rotary_dim, float eps, int write_kv, cudaStream_t stream) {
+                int value_dim, int rotary_dim, float eps, int write_kv, cudaStream_t stream) {
   // few tokens: 4 warps per CTA and enough CTAs per token to give every head a warp; many tokens: one CTA of 8
   // warps per token, so that the token's angles are computed once
   const int units = heads + 2 * kv_heads;
@@ -248,30 +252,30 @@ int launch_rope(T* qkv, const int* positions, const int* slot_mapping, const flo
   const int units_per_cta = many ? units : 4;
   const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
   const size_t smem = (size_t)rotary_dim * sizeof(float);
-  const bool paired = (head_dim % 2 == 0) && (rotary_dim % 4 == 0) && ((uintptr_t)qkv % (2 * sizeof(T)) == 0) &&
+  const bool paired = (head_dim % 2 == 0) && (value_dim % 2 == 0) && (rotary_dim % 4 == 0) && ((uintptr_t)qkv % (2 * sizeof(T)) == 0) &&
                       ((uintptr_t)k_pages % (2 * sizeof(T)) == 0);
   if (paired)
     return mir_launch("qk_rope_store", qk_rope_store_kernel<T, true>, grid, dim3(threads), smem, stream, 0, qkv, positions,
-                      slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, rotary_dim,
-                      eps, write_kv, units_per_cta);
+                      slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, value_dim,
+                      rotary_dim, eps, write_kv, units_per_cta);
   return mir_launch("qk_rope_store", qk_rope_store_kernel<T, false>, grid, dim3(threads), smem, stream, 0, qkv, positions,
-                    slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, rotary_dim, eps,
-                    write_kv, units_per_cta);
+                    slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, value_dim,
+                    rotary_dim, eps, write_kv, units_per_cta);
 }
 
 MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, const int* slot_mapping,
                                  const float* inv_freq, const float* q_norm, const float* k_norm, void* k_pages,
-                                 void* v_pages, int tokens, int heads, int kv_heads, int head_dim, int rotary_dim,
-                                 float eps, int write_kv, cudaStream_t stream) {
+                                 void* v_pages, int tokens, int heads, int kv_heads, int head_dim, int value_dim,
+                                 int rotary_dim, float eps, int write_kv, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
-  if (tokens < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim ||
+  if (tokens < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || value_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim ||
       (rotary_dim & 1)) {
     mir_set_error("qk_rope_store: bad sizes (heads %d, kv heads %d, head_dim %d, rotary_dim %d)", heads, kv_heads,
                   head_dim, rotary_dim);
     return MIR_BAD_ARGUMENT;
   }
   if (rotary_dim > 8192) { mir_set_error("qk_rope_store: rotary_dim %d is too large", rotary_dim); return MIR_BAD_ARGUMENT; }
-  if (bf16 && rotary_dim == head_dim && head_dim % 16 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 &&
+  if (bf16 && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 &&
       ((uintptr_t)v_pages & 15) == 0) {
     __nv_bfloat16* q = (__nv_bfloat16*)qkv;
     __nv_bfloat16* kp = (__nv_bfloat16*)k_pages;
@@ -287,7 +291,8 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
   }
   if (bf16)
     return launch_rope((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (__nv_bfloat16*)k_pages,
-                       (__nv_bfloat16*)v_pages, tokens, heads, kv_heads, head_dim, rotary_dim, eps, write_kv, stream);
+                       (__nv_bfloat16*)v_pages, tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps, write_kv,
+                       stream);
   return launch_rope((float*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (float*)k_pages, (float*)v_pages,
-                     tokens, heads, kv_heads, head_dim, rotary_dim, eps, write_kv, stream);
+                     tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps, write_kv, stream);
 }

@@ -112,6 +112,7 @@ class StepContext(PartContext):
     single_rows: int = 0
     single_context: int = 0
     page_size: int = 0
+    previous_tokens: Optional[torch.Tensor] = None   # int32 [T]: the token before each token in its request, -1 at its start
     # (residual data_ptr, rows, sums-of-squares tensor, tiles, weighted rows, norm weight data_ptr) or None
     residual_stats: Optional[tuple] = None
     # The norm that will be applied to the residual right after the part that runs now has added into it (set by

@@ -75,7 +75,8 @@ class DecodeGraph:
         options_ints = rows * kernels.SAMPLE_OPTIONS.itemsize // 4
         # host-written block: sampling options (first: they hold 64-bit values and the block starts on a
         # 256-byte boundary), tokens, positions, state slots, one table per group
-        sizes = [options_ints, rows, rows, rows] + [rows * w for w in widths]
+        self.pairs = runner.model.spec.embedding.pairs is not None       # the embedding also reads the token before
+        sizes = [options_ints, rows, rows, rows] + [rows * w for w in widths] + ([rows] if self.pairs else [])
         self._offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
         upload = int(self._offsets[-1])
         # device-computed block: slot mapping per group, context lengths, and the constant index arrays
@@ -88,6 +89,7 @@ class DecodeGraph:
         self.options = cut(0).view(torch.uint8)
         self.tokens, self.positions, self.state_slots = cut(1), cut(2), cut(3)
         self.tables = [cut(4 + g).view(rows, widths[g]) for g in range(groups)]
+        self.previous = cut(4 + groups) if self.pairs else None
         cursor = upload
         self.slot_mappings = []
         for _ in range(groups):
@@ -137,7 +139,7 @@ class DecodeGraph:
             dtype=runner.model.env.dtype, host_query_starts=list(range(self.rows + 1)),
             host_start_positions=[0] * self.rows, host_state_slots=[0] * self.rows,
             max_context=max(self.widths) * page if self.widths else 0, max_portion=1, decode_only=True,
-            page_size=page)
+            page_size=page, previous_tokens=self.previous)
 
     def _body(self) -> None:
         runner = self.runner
@@ -149,7 +151,8 @@ class DecodeGraph:
         residual = runner.model.forward(ctx)
         self.logits = runner.model.logits(ctx, residual, self.want_rows, candidates=self.candidates)
         kernels.sample(self.logits, self.options, self.sampled, self.sort_keys, self.ranked, self.candidates)
-        kernels.decode_advance(self.sampled, self.tokens, self.positions, self.token_log, self.step_counter)
+        kernels.decode_advance(self.sampled, self.tokens, self.positions, self.token_log, self.step_counter,
+                               self.previous)
 
     def _capture(self) -> None:
         # every row is padding while warming up and capturing: nothing is written to the cache
@@ -184,6 +187,8 @@ class DecodeGraph:
         host_tokens[:n] = tokens
         host_positions[:n] = [seq.length for seq in sequences]
         host_slots[:n] = [seq.slot for seq in sequences]
+        if self.pairs:
+            self._host_part(4 + len(self.widths))[:n] = [seq.last_token if seq.length > 0 else -1 for seq in sequences]
         if n != self._live_rows:                   # (the padding rows are as the last call left them otherwise)
             host_tokens[n:] = 0
             host_positions[n:] = -1

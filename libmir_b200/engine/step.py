@@ -137,6 +137,9 @@ class StepRunner:
         rows = len(entries)
         single_rows = sum(1 for c in counts if c == 1)
         tokens = np.empty(total, dtype=np.int32)
+        # the token before each token in its request (-1 at a request's start), for embeddings that look at pairs
+        pairs = self.model.spec.embedding.pairs is not None
+        previous = np.empty(total if pairs else 0, dtype=np.int32)
         positions = np.empty(total, dtype=np.int32)
         row_of_token = np.empty(total, dtype=np.int32)
         query_starts = np.zeros(rows + 1, dtype=np.int32)
@@ -150,6 +153,11 @@ class StepRunner:
             if ids.size and (ids.min() < 0 or ids.max() >= vocab):
                 raise SchedulerError(f"request {entry.request_id!r}: token id outside [0, {vocab})")
             tokens[cursor:cursor + count] = ids
+            if pairs:
+                if seq.length > 0 and seq.last_token < 0:
+                    raise SchedulerError(f"request {entry.request_id!r}: the token fed last is not known on the host")
+                previous[cursor] = seq.last_token if seq.length > 0 else -1
+                previous[cursor + 1:cursor + count] = ids[:-1]
             positions[cursor:cursor + count] = np.arange(seq.length, seq.length + count, dtype=np.int32)
             row_of_token[cursor:cursor + count] = r
             query_starts[r + 1] = cursor + count
@@ -183,6 +191,8 @@ class StepRunner:
                 pages = table[r, pos // page]
                 slots[begin:end] = np.where(pages >= 0, pages * page + pos % page, -1)
             arrays += [table, slots]
+        if pairs:
+            arrays.append(previous)
         staged = self._stage(arrays)
         groups = []
         for g, width in enumerate(widths):
@@ -196,7 +206,7 @@ class StepRunner:
             host_state_slots=state_slots.tolist(), max_context=int(context_lens.max()) if rows else 0,
             max_portion=max(counts) if counts else 0, decode_only=all(c == 1 for c in counts),
             single_rows=single_rows, single_context=int(context_lens[:single_rows].max()) if single_rows else 0,
-            page_size=page)
+            page_size=page, previous_tokens=staged[-1] if pairs else None)
         return ctx, staged[6], want_keys
 
     # -- the step ----------------------------------------------------------------------
@@ -388,8 +398,9 @@ class StepRunner:
             graph.replay()
         tokens = graph.token_log[:steps, :len(entries)].cpu()
         graph.step_counter.zero_()
-        for entry, seq in zip(ahead, sequences):      # (the sampled ids stayed on the device: no tokens to remember)
+        for row, (entry, seq) in enumerate(zip(ahead, sequences)):   # (no ids for the prefix cache to remember)
             self.manager.commit(seq, seq.length + len(entry.tokens))
+            seq.last_token = int(tokens[steps - 2, row]) if steps >= 2 else int(entry.tokens[0])
         self.steps += steps
         self.tokens_run += steps * len(entries)
         return tokens

@@ -30,17 +30,28 @@ _SIGNATURES = {
         "mir_add_bias": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "mir_cast": [c_int, c_void_p, c_void_p, c_size_t, c_void_p],
         "mir_qk_rope_store": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_paged_attention_generic": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                        c_void_p],
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                        c_int, c_void_p],
+        "mir_embed_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                            c_longlong, c_longlong, c_float, c_void_p],
+        "mir_gelu_tanh": [c_int, c_void_p, c_size_t, c_void_p],
+        "mir_add_normed_branches": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
+        "mir_short_conv_silu": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_delta_rule_scan": [c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p],
+        "mir_gated_head_norm": [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                c_int, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
         "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
                        c_void_p, c_int, c_void_p],
         "mir_repetition_penalty": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_decode_prepare": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
-        "mir_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
+        "mir_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
     },
     "bf16": {
         "mir_decode_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -289,6 +300,115 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: floa
                               table.shape[0], scale, _stream()))
 
 
+def embed_pairs(table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, previous: torch.Tensor, out: torch.Tensor,
+                mul_previous: int, mul_current: int, scale: float = 1.0) -> None:
+    """out[r] = float(table[ids[r]]) * scale + float(pairs[bucket]) with bucket = (previous[r] * mul_previous +
+    ids[r] * mul_current) mod (rows of pairs - 1), and the last row of `pairs` where previous[r] < 0 (a request's
+    first token)."""
+    _cuda(table, pairs, ids, previous, out)
+    rows, hidden = out.shape
+    _require(table.is_contiguous() and pairs.is_contiguous() and out.is_contiguous() and ids.dtype == torch.int32
+             and previous.dtype == torch.int32 and ids.numel() == rows and previous.numel() >= rows
+             and out.dtype == torch.float32 and table.shape[1] == hidden and pairs.shape[1] == hidden
+             and pairs.dtype == table.dtype and pairs.shape[0] >= 2, "embed_pairs: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_embed_pairs(_is_bf16(table), table.data_ptr(), pairs.data_ptr(), ids.data_ptr(),
+                                    previous.data_ptr(), out.data_ptr(), rows, hidden, table.shape[0],
+                                    pairs.shape[0] - 1, int(mul_previous), int(mul_current), scale, _stream()))
+
+
+def gelu_tanh(x: torch.Tensor) -> None:
+    """x <- 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))) in place, computed in 32-bit."""
+    _cuda(x)
+    _require(x.is_contiguous(), "gelu_tanh: a contiguous tensor is needed")
+    lib = library("core")
+    _check(lib, lib.mir_gelu_tanh(_is_bf16(x), x.data_ptr(), x.numel(), _stream()))
+
+
+def add_normed_branches(branches, weights, residual: torch.Tensor, eps: float, scale: float) -> None:
+    """residual += scale * sum_b rmsnorm(branches[b]) * weights[b]; every tensor 32-bit, branches [rows, hidden]."""
+    _cuda(residual, *branches, *weights)
+    rows, hidden = residual.shape
+    _require(1 <= len(branches) <= 4 and len(weights) == len(branches) and residual.dtype == torch.float32
+             and residual.is_contiguous(), "add_normed_branches: one to four branches and a 32-bit residual")
+    for branch, weight in zip(branches, weights):
+        _require(branch.dtype == torch.float32 and branch.shape == residual.shape and branch.is_contiguous()
+                 and weight.dtype == torch.float32 and weight.numel() == hidden and weight.is_contiguous(),
+                 "add_normed_branches: branches are float32 [rows, hidden], weights float32 [hidden]")
+    pointers = (c_void_p * len(branches))(*[b.data_ptr() for b in branches])
+    weight_pointers = (c_void_p * len(weights))(*[w.data_ptr() for w in weights])
+    lib = library("core")
+    _check(lib, lib.mir_add_normed_branches(pointers, weight_pointers, len(branches), residual.data_ptr(), rows, hidden,
+                                            eps, scale, _stream()))
+
+
+def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, row_of_token: torch.Tensor,
+                    query_starts: torch.Tensor, state_slots: torch.Tensor, positions: torch.Tensor,
+                    out: torch.Tensor) -> None:
+    """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) within each request, 32-bit: x is a column
+    range [tokens, channels] of the packed projection (a view with unit column stride), weight [channels, taps] with
+    the current token's tap last, tail [slots, taps - 1, channels] the request's last inputs (32-bit, zero at its
+    start), read for what lies before the portion and then moved on."""
+    _cuda(x, weight, tail, row_of_token, query_starts, state_slots, positions, out)
+    tokens, channels = x.shape
+    taps = weight.shape[1]
+    rows = query_starts.numel() - 1
+    _require(x.stride(1) == 1 and weight.is_contiguous() and weight.shape[0] == channels and weight.dtype == x.dtype
+             and tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape[1:] == (max(taps - 1, 0), channels)
+             and out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, channels),
+             "short_conv_silu: shapes or dtypes do not fit")
+    _require(all(t.dtype == torch.int32 for t in (row_of_token, query_starts, state_slots, positions)),
+             "short_conv_silu: the batch description is int32")
+    lib = library("core")
+    _check(lib, lib.mir_short_conv_silu(_is_bf16(x), x.data_ptr(), x.stride(0), weight.data_ptr(), tail.data_ptr(),
+                                        row_of_token.data_ptr(), query_starts.data_ptr(), state_slots.data_ptr(),
+                                        positions.data_ptr(), out.data_ptr(), tokens, rows, channels, taps, _stream()))
+
+
+def delta_rule_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, decay_raw: torch.Tensor, dt_bias: torch.Tensor,
+                    a_log: torch.Tensor, state: torch.Tensor, query_starts: torch.Tensor, state_slots: torch.Tensor,
+                    positions: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
+                    value_dim: int, per_channel: bool) -> None:
+    """The gated delta rule over the tokens of each request row, from and into state [slots, heads, value_dim,
+    key_dim] (32-bit).  qkv [tokens, 2 kv_heads key_dim + heads value_dim] 32-bit (q | k | v after convolution);
+    beta_raw [tokens, heads] and decay_raw [tokens, heads] or [tokens, heads * key_dim] (one decay per key channel)
+    are views with unit column stride, before sigmoid / softplus; out [tokens, heads * value_dim] 32-bit."""
+    _cuda(qkv, beta_raw, decay_raw, dt_bias, a_log, state, query_starts, state_slots, positions, out)
+    tokens = qkv.shape[0]
+    rows = query_starts.numel() - 1
+    _require(qkv.dtype == torch.float32 and qkv.is_contiguous()
+             and qkv.shape[1] == 2 * kv_heads * key_dim + heads * value_dim and out.dtype == torch.float32
+             and out.is_contiguous() and out.shape == (tokens, heads * value_dim), "delta_rule_scan: bad qkv or out")
+    _require(beta_raw.shape == (tokens, heads) and beta_raw.stride(1) == 1 and decay_raw.stride(1) == 1
+             and decay_raw.shape == (tokens, heads * key_dim if per_channel else heads)
+             and dt_bias.dtype == torch.float32 and dt_bias.numel() == decay_raw.shape[1] and dt_bias.is_contiguous()
+             and a_log.dtype == torch.float32 and a_log.numel() == heads, "delta_rule_scan: bad gates")
+    _require(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, value_dim, key_dim),
+             "delta_rule_scan: the state is float32 [slots, heads, value_dim, key_dim]")
+    _require(decay_raw.dtype in (beta_raw.dtype, torch.float32), "delta_rule_scan: bad decay dtype")
+    lib = library("core")
+    _check(lib, lib.mir_delta_rule_scan(_is_bf16(beta_raw), int(decay_raw.dtype == torch.float32), int(per_channel),
+                                        qkv.data_ptr(), beta_raw.data_ptr(), beta_raw.stride(0), decay_raw.data_ptr(),
+                                        decay_raw.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(),
+                                        query_starts.data_ptr(), state_slots.data_ptr(), positions.data_ptr(),
+                                        out.data_ptr(), rows, heads, kv_heads, key_dim, value_dim, _stream()))
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int,
+                    value_dim: int, eps: float, sigmoid_gate: bool) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h]) per head, act = sigmoid or silu; o 32-bit
+    [tokens, heads * value_dim], gate a view with unit column stride, out contiguous in gate's dtype."""
+    _cuda(o, gate, weight, out)
+    tokens = o.shape[0]
+    _require(o.dtype == torch.float32 and o.is_contiguous() and o.shape[1] == heads * value_dim
+             and gate.shape == o.shape and gate.stride(1) == 1 and out.shape == o.shape and out.is_contiguous()
+             and out.dtype == gate.dtype and weight.dtype == torch.float32 and weight.numel() == value_dim,
+             "gated_head_norm: shapes or dtypes do not fit")
+    lib = library("core")
+    _check(lib, lib.mir_gated_head_norm(_is_bf16(out), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
+                                        out.data_ptr(), tokens, heads, value_dim, eps, int(sigmoid_gate), _stream()))
+
+
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
              rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(x[rows[r] if rows else r]) * weight; x and weight are 32-bit."""
@@ -358,13 +478,14 @@ def decode_prepare(positions, block_table, page_size, slot_mapping, context_lens
                                        slot_mapping.data_ptr(), context_lens.data_ptr(), rows, _stream()))
 
 
-def decode_advance(sampled, tokens, positions, token_log, step_counter) -> None:
-    """tokens <- sampled, positions += 1, token_log[step] <- sampled, step += 1 (on the device)."""
+def decode_advance(sampled, tokens, positions, token_log, step_counter, previous=None) -> None:
+    """tokens <- sampled, positions += 1, token_log[step] <- sampled, step += 1 (on the device); with `previous`,
+    previous <- tokens first (for an embedding that looks at pairs of tokens)."""
     rows = tokens.numel()
     lib = library("core")
     _check(lib, lib.mir_decode_advance(sampled.data_ptr(), tokens.data_ptr(), positions.data_ptr(),
                                        token_log.data_ptr(), token_log.shape[0], step_counter.data_ptr(), rows,
-                                       _stream()))
+                                       _ptr(previous), _stream()))
 
 
 # --------------------------------------------------------------------------- attention
@@ -372,13 +493,15 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
                   inv_freq: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
                   k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], heads: int, kv_heads: int,
                   head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True,
-                  keys_in_place: bool = False) -> None:
+                  keys_in_place: bool = False, value_dim: Optional[int] = None) -> None:
     """q/k-norm + rotary on the packed qkv rows in place for q, k and v into their pages.  `keys_in_place`:
     the keys are normed and rotated in place like the queries and nothing is written to the pages."""
     write_kv = write_kv and not keys_in_place
     _cuda(qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages)
     tokens = qkv.shape[0]
-    _require(qkv.is_contiguous() and qkv.shape[1] == (heads + 2 * kv_heads) * head_dim, "qk_rope_store: bad qkv")
+    value_dim = head_dim if value_dim is None else value_dim
+    _require(qkv.is_contiguous() and qkv.shape[1] == (heads + kv_heads) * head_dim + kv_heads * value_dim,
+             "qk_rope_store: bad qkv")
     _require(positions.dtype == torch.int32 and positions.numel() >= tokens, "qk_rope_store: bad positions")
     _require(head_dim % 8 == 0, f"qk_rope_store: head_dim {head_dim} is not a multiple of 8")
     if rotary_dim:
@@ -394,18 +517,21 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
     lib = library("core")
     _check(lib, lib.mir_qk_rope_store(_is_bf16(qkv), qkv.data_ptr(), positions.data_ptr(), _ptr(slot_mapping),
                                       _ptr(inv_freq), _ptr(q_norm), _ptr(k_norm), _ptr(k_pages), _ptr(v_pages),
-                                      tokens, heads, kv_heads, head_dim, rotary_dim, eps,
+                                      tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps,
                                       2 if keys_in_place else int(write_kv), _stream()))
 
 
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
                             page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
-                            window: Optional[int]) -> None:
-    """out[t, h] = softmax over the visible cached keys of token t's request; q is read from the packed qkv rows."""
+                            window: Optional[int], value_dim: Optional[int] = None, keep_first: int = 0) -> None:
+    """out[t, h] = softmax over the visible cached keys of token t's request; q is read from the packed qkv rows.
+    `value_dim`: width of a value head (head_dim if None); `keep_first`: with a window, the request's first keys
+    that stay visible to every query."""
     _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions)
     tokens = out.shape[0]
-    _require(out.is_contiguous() and out.shape[1] == heads * head_dim and qkv.dtype == out.dtype
+    value_dim = head_dim if value_dim is None else value_dim
+    _require(out.is_contiguous() and out.shape[1] == heads * value_dim and qkv.dtype == out.dtype
              and k_pages.dtype == out.dtype and v_pages.dtype == out.dtype, "paged_attention: bad tensors")
     _require(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
              and row_of_token.dtype == torch.int32 and positions.dtype == torch.int32, "paged_attention: bad metadata")
@@ -413,7 +539,7 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
     _check(lib, lib.mir_paged_attention_generic(
         _is_bf16(out), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], row_of_token.data_ptr(), positions.data_ptr(), tokens,
-        page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream()))
+        page_size, heads, kv_heads, head_dim, value_dim, scale, int(window or 0), int(keep_first or 0), _stream()))
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel

@@ -39,6 +39,7 @@ class DecoderModel:
         self.blocks = [build_block(layer, env) for layer in spec.layers]
         self.final_norm = build_part(spec.final_norm, env)
         self.embedding: Optional[torch.Tensor] = None
+        self.pair_embedding: Optional[torch.Tensor] = None      # the table of token pairs, if the model has one
         self.head: Optional[torch.Tensor] = None
         self._runs_key, self._runs_list, self._native = None, [], {}
 
@@ -63,6 +64,9 @@ class DecoderModel:
         spec = self.spec
         table: Dict[str, Tuple[object, str, ParamSpec]] = {}
         table[spec.embedding.name] = (self, "embedding", ParamSpec((spec.embedding.vocab_size, spec.embedding.hidden_size)))
+        if spec.embedding.pairs is not None:
+            pairs = spec.embedding.pairs
+            table[pairs.name] = (self, "pair_embedding", ParamSpec((pairs.buckets + 1, spec.embedding.hidden_size)))
         for layer_spec, block in zip(spec.layers, self.blocks):
             for slot, part in block.parts():
                 for local, param in part.parameters().items():
@@ -82,12 +86,19 @@ class DecoderModel:
         for owner, local_tensors in per_owner.values():
             if owner is self:
                 self.embedding = local_tensors["embedding"].contiguous()
+                if "pair_embedding" in local_tensors:
+                    self.pair_embedding = local_tensors["pair_embedding"].contiguous()
                 self.head = local_tensors.get("head")
             else:
                 owner.bind(local_tensors)
         if self.spec.head.tied:
             self.head = self.embedding
         self.head = self.head.contiguous()
+        if self.spec.head.scale != 1.0:
+            # logits = scale * head . norm(x): the factor goes into the final norm's 32-bit weight, once
+            if not getattr(self.final_norm, "foldable", False):
+                raise ValueError("a head with a logit scale needs a final norm with a 32-bit weight to carry it")
+            self.final_norm.scale_weight(self.spec.head.scale)
         self._runs_key = None                       # descriptors of the layers hold pointers to the old tensors
 
     def parts(self) -> List[Part]:
@@ -116,7 +127,12 @@ class DecoderModel:
         """Run the tokens of the step; returns the 32-bit residual [T, H] after the last layer."""
         spec = self.spec
         residual = ctx.alloc((ctx.num_tokens, spec.hidden_size), torch.float32)
-        kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
+        if spec.embedding.pairs is not None:
+            pairs = spec.embedding.pairs
+            kernels.embed_pairs(self.embedding, self.pair_embedding, ctx.tokens, ctx.previous_tokens, residual,
+                                pairs.mul_previous, pairs.mul_current, spec.embedding.multiplier)
+        else:
+            kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
         for run in self._runs(ctx):
             if run.layers is not None:
                 run.execute(ctx, residual)

@@ -4,6 +4,10 @@ pre_norm:  x += mixer(norm_1(x));  x += feed_forward(norm_2(x))
 (metal/src/engine/dense/swiglu/layer.rs:123-166).  The residual stream x is 32-bit; each branch adds
 its result into it (the matrix product's accumulate epilogue), so no separate add kernel runs.
 A layer without feed-forward, or without one of the norms, leaves that step out.
+
+parallel:  h = norm_1(x);  x += mixer(h) + feed_forward(h)
+One norm, and both branches read its output; each adds its result into the 32-bit residual, so the sum
+x + mixer(h) + feed_forward(h) is formed in 32-bit whatever the engine's dtype.
 """
 
 from __future__ import annotations
@@ -49,6 +53,8 @@ class PreNormBlock(Block):
             return None
         if ff is not None and (type(ff) is not SwiGlu or type(self.feed_forward_norm) is not RmsNorm):
             return None
+        if mixer.spec.value_dim != mixer.spec.head_dim or (mixer.spec.window is not None and mixer.spec.keep_first):
+            return None                      # the executor knows neither a value width of its own nor kept first tokens
         rotation = mixer.position.rotation() if mixer.position is not None else (None, 0)
         if rotation is None or self.env.dtype not in (torch.bfloat16, torch.float32):
             return None
@@ -98,7 +104,41 @@ class PreNormBlock(Block):
         return norm.forward(ctx, residual)
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock}
+class ParallelBlock(Block):
+    """x += mixer(norm(x)) + feed_forward(norm(x)): the norm runs once and both branches read its output."""
+
+    SLOTS = ("mixer_norm", "mixer", "feed_forward")
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.feed_forward_norm is not None:
+            raise ValueError("the parallel arrangement has one norm: feed_forward_norm must be None")
+        self.mixer_norm = build_part(spec.mixer_norm, env)
+        self.mixer = build_part(spec.mixer, env)
+        self.feed_forward = build_part(spec.feed_forward, env)
+
+    def parts(self):
+        return [(slot, getattr(self, slot)) for slot in self.SLOTS if getattr(self, slot) is not None]
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement()
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def forward(self, ctx, cache, residual):
+        # the residual changes twice before the next norm sees it, and the normed rows are read twice: the norm runs
+        # as a kernel, and no product prepares the next one
+        x = (self.mixer_norm.forward(ctx, residual) if self.mixer_norm is not None else ctx.cast_residual(residual))
+        ctx.residual_stats = None
+        ctx.upcoming_norm = None
+        self.mixer.forward(ctx, cache, x, residual)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(ctx, x, residual)
+        ctx.residual_stats = None
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock}
 
 
 def build_block(layer_spec, env):

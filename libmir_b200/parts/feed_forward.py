@@ -1,4 +1,5 @@
-"""Dense SwiGLU feed-forward: down(silu(gate(x)) * up(x)), accumulated into the 32-bit residual.
+"""Dense feed-forwards.  SwiGLU: down(silu(gate(x)) * up(x)), accumulated into the 32-bit residual; and the plain
+two-matrix form with the tanh GELU (GeluMlp, at the end of the file).
 
 Gate and up are one product on row-stacked [Wg; Wu] whose output row is [gate | up], as libmir's CUDA
 engine does (cuda/src/backend/linear/pair.rs:36-64, cuda/src/backend/dense/feed_forward.rs:108-150).
@@ -43,3 +44,32 @@ class SwiGlu(FeedForward):
         hidden = ctx.alloc((tokens, s.intermediate_size), self.env.dtype)
         kernels.gate_up_silu(x, self.w_gate_up, hidden, ctx.alloc)
         ctx.accumulate(hidden, self.w_down, residual)      # may also prepare the norm that follows
+
+
+class GeluMlp(FeedForward):
+    """down(gelu_tanh(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit on the
+    product's rows, in place."""
+
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.w_up = self.w_down = None
+
+    def parameters(self):
+        s = self.spec
+        return {"up": ParamSpec((s.intermediate_size, s.hidden_size)),
+                "down": ParamSpec((s.hidden_size, s.intermediate_size))}
+
+    def bind(self, tensors):
+        self.w_up = tensors["up"].contiguous()
+        self.w_down = tensors["down"].contiguous()
+
+    def weight_bytes(self):
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, ctx, x, residual):
+        hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)
+        kernels.linear(x, self.w_up, hidden, alloc=ctx.alloc)
+        kernels.gelu_tanh(hidden)
+        ctx.accumulate(hidden, self.w_down, residual)

@@ -1,4 +1,5 @@
-"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, no (1 + w) form.
+"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * (offset + w); offset 0 is the plain form, offset 1 the form whose
+weight is stored around zero (the sum is formed once, in 32-bit, when the weight is bound).
 
 libmir cuda/kernels/rms_norm_bf16.cu:3-36; eps key and aliases models/src/layout/decoder/parse/mod.rs:82-86.
 The input is the 32-bit residual stream; the weight is kept in 32-bit (exact for every stored dtype).
@@ -24,10 +25,16 @@ class RmsNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def parameters(self):
-        return {"weight": ParamSpec((self.spec.size,), init="ones", store="float32")}
+        init = "zeros" if self.spec.offset else "ones"
+        return {self.spec.tensor: ParamSpec((self.spec.size,), init=init, store="float32")}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        weight = tensors[self.spec.tensor].contiguous()
+        self.weight = weight + self.spec.offset if self.spec.offset else weight
+
+    def scale_weight(self, factor: float) -> None:
+        """Multiply the bound weight by a constant (a model's logit scale carried by its final norm)."""
+        self.weight = (self.weight * factor).contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * 4

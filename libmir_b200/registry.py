@@ -34,6 +34,9 @@ def known_architectures() -> list:
 
 
 def architecture_of(config_json: Mapping) -> str:
+    single = config_json.get("architecture")
+    if isinstance(single, str) and "architectures" not in config_json:
+        return single                                      # configurations that name one class as a string
     names = config_json.get("architectures")
     if not isinstance(names, list) or not names or not all(isinstance(n, str) for n in names):
         raise ConfigError("config.json must name the model class in `architectures`, e.g. [\"LlamaForCausalLM\"]; "

@@ -577,7 +577,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                          const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
-                         float scale_log2, int window) {
+                         float scale_log2, int window, int keep_first) {
   constexpr int STRIDE = D + 8;
   constexpr int TILE_ELEMS = kKeyTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -636,17 +636,26 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   const int warp_last = min(first_position + warp * 16 + 15, last_position);
   const int warp_first = min(first_position + warp * 16, last_position);
   const int warp_first_key = (window > 0 && warp_first + 1 > window) ? warp_first + 1 - window : 0;
+  // With a window, the request's first keep_first keys stay visible: the tiles that hold those of them that lie
+  // before the window's first tile are walked first (key_begin is a multiple of the tile, so the two runs of tiles
+  // never overlap), then the window's tiles.  Tile i of the walk starts at key tile_key(i).
+  const int kept_keys = (window > 0 && keep_first > 0) ? min(keep_first, key_begin) : 0;
+  const int kept_tiles = (kept_keys + kKeyTile - 1) / kKeyTile;
+  const int total_tiles = kept_tiles + (key_end - key_begin + kKeyTile - 1) / kKeyTile;
+  auto tile_key = [&](int i) { return i < kept_tiles ? i * kKeyTile : key_begin + (i - kept_tiles) * kKeyTile; };
+  auto tile_limit = [&](int i) { return i < kept_tiles ? kept_keys : key_end; };
 
   load_tile<D, kKeyTile, kPrefillWarps * 32>(buffers, buffers + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
-                         key_begin, key_end, threadIdx.x);
+                         tile_key(0), tile_limit(0), threadIdx.x);
   cp_async_commit();
   int stage = 0;
-  for (int key0 = key_begin; key0 < key_end; key0 += kKeyTile, stage ^= 1) {
-    const int next = key0 + kKeyTile;
-    if (next < key_end) {
+  for (int tile = 0; tile < total_tiles; ++tile, stage ^= 1) {
+    const int key0 = tile_key(tile);
+    const bool kept_tile = tile < kept_tiles;
+    if (tile + 1 < total_tiles) {
       bf16* dst = buffers + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_tile<D, kKeyTile, kPrefillWarps * 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head, next,
-                             key_end, threadIdx.x);
+      load_tile<D, kKeyTile, kPrefillWarps * 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
+                             tile_key(tile + 1), tile_limit(tile + 1), threadIdx.x);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -654,8 +663,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
     const bf16* k_tile = buffers + stage * 2 * TILE_ELEMS;
     const bf16* v_tile = k_tile + TILE_ELEMS;
     // this warp needs the tile only if some key of it is visible to some of its rows
-    if (key0 <= warp_last && key0 + kKeyTile > warp_first_key) {
-      const bool needs_mask = key0 + kKeyTile - 1 > warp_first || (window > 0 && key0 < warp_last + 1 - window + 15);
+    if (kept_tile || (key0 <= warp_last && key0 + kKeyTile > warp_first_key)) {
+      const bool needs_mask = kept_tile || key0 + kKeyTile - 1 > warp_first ||
+                              (window > 0 && key0 < warp_last + 1 - window + 15);
       constexpr int NT = kKeyTile / 8;
       float s[NT][4];
 #pragma unroll
@@ -669,7 +679,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
           if (needs_mask) {
             const int key = key0 + nt * 8 + c + (e & 1);
             const int pos = (e < 2) ? pos0 : pos1;
-            visible = key <= pos && (window <= 0 || key > pos - window);
+            visible = key <= pos && (window <= 0 || key > pos - window || key < keep_first);
           }
           s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
         }
@@ -760,7 +770,7 @@ template <int D>
 int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                    const int* block_table, int table_width, const int* query_starts, const int* context_lens,
                    int num_rows, int tokens, int page_size, int heads, int kv_heads, float scale, int window,
-                   cudaStream_t stream) {
+                   int keep_first, cudaStream_t stream) {
   const size_t smem = (size_t)2 * 2 * kKeyTile * (D + 8) * sizeof(bf16);
   static bool smem_set = false;
   int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention", smem_set);
@@ -772,7 +782,8 @@ int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_page
   }
   return mir_launch("prefill_attention", prefill_attention_kernel<D>, dim3(heads, tiles), dim3(kPrefillWarps * 32),
                     smem, stream, 0, q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
-                    context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window);
+                    context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
+                    keep_first);
 }
 
 bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int page_size, int table_width, int window) {
@@ -853,13 +864,15 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
 
 // Any mix of portions: row r has tokens query_starts[r] .. query_starts[r+1]-1 of the packed batch, and its
 // request holds context_lens[r] tokens after this step (so the portion starts at context_lens[r] - count).
-MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                          const void* v_pages, const int* block_table, int table_width,
-                                          const int* query_starts, const int* context_lens, int num_rows, int tokens,
-                                          int page_size, int heads, int kv_heads, int head_dim, float scale,
-                                          int window, cudaStream_t stream) {
+// keep_first: with a window, the first keys of every request that stay visible to all its later queries.
+MIR_EXPORT int mir_prefill_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                               const void* v_pages, const int* block_table, int table_width,
+                                               const int* query_starts, const int* context_lens, int num_rows,
+                                               int tokens, int page_size, int heads, int kv_heads, int head_dim,
+                                               float scale, int window, int keep_first, cudaStream_t stream) {
   if (tokens == 0 || num_rows == 0) return MIR_OK;
-  if (bad_common("prefill_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
+  if (bad_common("prefill_attention", heads, kv_heads, head_dim, page_size, table_width, window) || keep_first < 0)
+    return MIR_BAD_ARGUMENT;
   if (tokens < 0 || num_rows < 0) {
     mir_set_error("prefill_attention: bad tokens %d, rows %d or heads %d", tokens, num_rows, heads);
     return MIR_BAD_ARGUMENT;
@@ -867,10 +880,20 @@ MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, voi
   if (head_dim == 64)
     return launch_prefill<64>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                               block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
-                              kv_heads, scale, window, stream);
+                              kv_heads, scale, window, keep_first, stream);
   return launch_prefill<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                              block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
-                             kv_heads, scale, window, stream);
+                             kv_heads, scale, window, keep_first, stream);
+}
+
+MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                          const void* v_pages, const int* block_table, int table_width,
+                                          const int* query_starts, const int* context_lens, int num_rows, int tokens,
+                                          int page_size, int heads, int kv_heads, int head_dim, float scale,
+                                          int window, cudaStream_t stream) {
+  return mir_prefill_attention_kept_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
+                                         context_lens, num_rows, tokens, page_size, heads, kv_heads, head_dim, scale,
+                                         window, 0, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -75,7 +75,7 @@ class DecodeGraph:
         options_ints = rows * kernels.SAMPLE_OPTIONS.itemsize // 4
         # host-written block: sampling options (first: they hold 64-bit values and the block starts on a
         # 256-byte boundary), tokens, positions, state slots, one table per group
-        self.pairs = runner.model.spec.embedding.pairs is not None       # the embedding also reads the token before
+        self.pairs = getattr(getattr(runner.model.spec, "embedding", None), "pairs", None) is not None       # the embedding also reads the token before
         sizes = [options_ints, rows, rows, rows] + [rows * w for w in widths] + ([rows] if self.pairs else [])
         self._offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
         upload = int(self._offsets[-1])

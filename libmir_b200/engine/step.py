@@ -138,7 +138,7 @@ class StepRunner:
         single_rows = sum(1 for c in counts if c == 1)
         tokens = np.empty(total, dtype=np.int32)
         # the token before each token in its request (-1 at a request's start), for embeddings that look at pairs
-        pairs = self.model.spec.embedding.pairs is not None
+        pairs = getattr(getattr(self.model.spec, "embedding", None), "pairs", None) is not None
         previous = np.empty(total if pairs else 0, dtype=np.int32)
         positions = np.empty(total, dtype=np.int32)
         row_of_token = np.empty(total, dtype=np.int32)

@@ -69,6 +69,9 @@ _SIGNATURES = {
         "mir_decode_attention_tc_error": [],
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mir_prefill_attention_kept_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                            c_void_p],
         "mir_prefill_attention_tc_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                           c_void_p],
@@ -597,10 +600,11 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
                       block_table: torch.Tensor, query_starts: torch.Tensor, context_lens: torch.Tensor,
                       page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                       window: Optional[int], tensor_cores: Optional[bool] = None,
-                      portion_tokens: Optional[int] = None) -> None:
+                      portion_tokens: Optional[int] = None, keep_first: int = 0) -> None:
     """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]
     of the packed qkv and out; the rows may be a part of the batch, `portion_tokens` then says how many tokens
-    they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses."""
+    they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses.
+    `keep_first`: with a window, the first keys of a request that every later query still sees (mma.sync kernel)."""
     _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens)
     tokens = out.shape[0]
     rows = context_lens.numel()
@@ -611,6 +615,10 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
              and context_lens.dtype == torch.int32 and query_starts.numel() == rows + 1
              and block_table.shape[0] >= rows, "prefill_attention: bad metadata")
     lib = library("bf16")
+    keep_first = int(keep_first or 0) if window else 0
+    if keep_first:
+        _require(not tensor_cores, "prefill_attention: kept first keys run the mma.sync kernel")
+        tensor_cores = False
     if tensor_cores is None:
         portion_tokens = tokens if portion_tokens is None else portion_tokens
         tensor_cores = (PREFILL_TENSOR_CORES and portion_tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
@@ -624,10 +632,10 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
             block_table.data_ptr(), block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens,
             page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream()))
         return
-    _check(lib, lib.mir_prefill_attention_bf16(
+    _check(lib, lib.mir_prefill_attention_kept_bf16(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
-        kv_heads, head_dim, scale, int(window or 0), _stream()))
+        kv_heads, head_dim, scale, int(window or 0), keep_first, _stream()))
 
 
 def set_prefill_softmax_streams(streams: int) -> None:

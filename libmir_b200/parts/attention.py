@@ -138,8 +138,16 @@ class SoftmaxAttention(Mixer):
         bfloat16 with head_dim 64 or 128 runs on tensor cores (split over the keys when every row is a
         single decoded token), everything else runs the reference kernel."""
         s = self.spec
-        plain = s.value_dim == s.head_dim and not (s.window is not None and s.keep_first)
-        if self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and plain:
+        kept = s.keep_first if s.window is not None else 0
+        fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
+        if fast and kept:
+            # kept first keys: the mma.sync tile kernel walks the kept tiles, then the window's, for every row of the
+            # batch (a decoded token is a portion of one token); the split-key decode kernels do not know kept keys
+            kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.query_starts,
+                                      ctx.context_lens, cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale,
+                                      s.window, tensor_cores=False, keep_first=kept)
+            return
+        if fast:
             # the single-token rows come first in the batch: they run as decoded tokens (keys split over CTAs, the
             # heads of a KV group in one CTA), the prompt portions after them as tiles of queries
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows

@@ -1,0 +1,113 @@
+"""Tiny Doderax configurations for the tests, and model folders with weights that make every mechanism matter.
+The configurations differ from one another in every size, in the order and kinds of layers, in windows, kept
+first tokens, taps, ranks and constants; some take values that make two sizes equal or 1."""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+
+def _left(heads, kv_heads, dim, vdim, scale, rot=None, mask=None):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot:
+        mixer["rot"] = {"dims": rot[0], "base": rot[1]}
+    if mask:
+        mixer["mask"] = {"size": mask[0], "keep_first": mask[1]}
+    return mixer
+
+
+def _right(heads, kv_heads, dim, vdim, conv):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+def _layer(kind, mixer, ff):
+    return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+DODERAX_X = {   # mixed layers; value heads wider than key heads; a window with kept first tokens; key heads of 24 and 40
+    "architecture": "Doderax", "vocab": 211, "width": 96, "logit_scale": 0.5, "norm": {"eps": 1e-6},
+    "embedding": {"bigram": {"buckets": 97, "mul_prev": 31, "mul_cur": 7}},
+    "layers": [
+        _layer("parallel", {"left": _left(4, 2, 32, 48, 0.2, rot=(16, 10000.0), mask=(20, 3)),
+                            "right": _right(4, 2, 24, 16, 3)}, 160),
+        _layer("channel_delta", _right(3, 3, 40, 24, 4), 128),
+        _layer("channel_delta", _right(4, 1, 32, 8, 2), 0),
+        _layer("parallel", {"left": _left(2, 1, 64, 64, 0.125, rot=(64, 500.0), mask=(33, 0)),
+                            "right": _right(2, 2, 64, 40, 4)}, 104),
+    ],
+}
+
+DODERAX_Y = {   # sizes that are equal or 1: one head, one tap, no window, no pair table, no logit scale, no feed-forward
+    "architecture": "Doderax", "vocab": 130, "width": 64, "norm": {"eps": 1e-5},
+    "layers": [
+        _layer("parallel", {"left": _left(2, 2, 16, 16, 0.25, rot=(8, 100.0)), "right": _right(1, 1, 32, 32, 1)}, 0),
+        _layer("channel_delta", _right(1, 1, 8, 64, 4), 64),
+        _layer("parallel", {"left": _left(1, 1, 24, 8, 0.3, mask=(5, 1)), "right": _right(2, 1, 16, 16, 5)}, 72),
+    ],
+}
+
+DODERAX_Z = {   # a window shorter than a page beside kept tokens that span pages; a key head of 200 channels
+    "architecture": "Doderax", "vocab": 150, "width": 80, "logit_scale": 2.0, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 64, "mul_prev": 5, "mul_cur": 11}},
+    "layers": [
+        _layer("parallel", {"left": _left(3, 3, 40, 24, 0.16, rot=(20, 250.0), mask=(9, 20)),
+                            "right": _right(2, 2, 200, 8, 4)}, 96),
+        _layer("parallel", {"left": _left(6, 2, 16, 32, 0.25, rot=(16, 10000.0), mask=(64, 2)),
+                            "right": _right(6, 3, 16, 16, 2)}, 0),
+    ],
+}
+
+DODERAX_W = {   # key and value heads of 64 and of 128 with kept first tokens: in bfloat16 the tensor-core tile kernel
+    "architecture": "Doderax", "vocab": 180, "width": 128, "logit_scale": 1.5, "norm": {"eps": 1e-6},
+    "embedding": {"bigram": {"buckets": 50, "mul_prev": 3, "mul_cur": 1}},
+    "layers": [
+        _layer("parallel", {"left": _left(4, 2, 64, 64, 0.125, rot=(32, 10000.0), mask=(70, 5)),
+                            "right": _right(2, 1, 32, 64, 4)}, 192),
+        _layer("channel_delta", _right(2, 2, 128, 16, 3), 0),
+        _layer("parallel", {"left": _left(2, 1, 128, 128, 0.09, rot=(128, 1000.0), mask=(40, 66)),
+                            "right": _right(4, 4, 16, 32, 2)}, 160),
+    ],
+}
+
+ALL = {"W": DODERAX_W, "X": DODERAX_X, "Y": DODERAX_Y, "Z": DODERAX_Z}
+PAGE_SIZES = {"W": 16, "X": 8, "Y": 16, "Z": 8}
+
+
+def make_folder(tmp_path, config: dict, seed: int, dtype: str, sharpen: float = 4.0) -> Path:
+    """config.json + model.safetensors.  The random weights of the package's writer are rescaled so that decays,
+    gates, convolutions, norm weights and attention scores are far from their neutral values: a lost state, a tap
+    read from the wrong token, a window one token off or a missing kept token then changes the logits well beyond
+    the tolerances."""
+    from libmir_b200.weights import load_tensor, read_catalog, write_file, write_model_folder
+    folder = write_model_folder(Path(tmp_path), config, seed=seed, dtype=dtype)
+    tensors = {name: load_tensor(entry) for name, entry in read_catalog(folder).items()}
+    generator = torch.Generator().manual_seed(seed + 1000)
+    normal = lambda shape, deviation: torch.randn(shape, generator=generator) * deviation
+    for name, tensor in list(tensors.items()):
+        kind = tensor.dtype
+        last = name.rsplit(".", 1)[-1]
+        if name.endswith(".conv"):
+            new = normal(tensor.shape, 0.6)
+        elif last == "A_log":
+            new = torch.rand(tensor.shape, generator=generator) * 2.0 - 1.5
+        elif last == "dt_bias":
+            new = normal(tensor.shape, 1.0)
+        elif last in ("norm", "out"):
+            new = 1.0 + normal(tensor.shape, 0.25)
+        elif last == "norm1" or name == "final.norm":
+            new = normal(tensor.shape, 0.25)
+        elif last in ("a", "b", "a1", "a2", "g1", "g2"):
+            new = tensor.float() * 3.0
+        elif last in ("q", "k") and ".left." in name:
+            new = tensor.float() * sharpen
+        elif last in ("o", "down"):
+            new = tensor.float() * 2.0
+        elif name == "head":
+            new = tensor.float() * 5.0
+        else:
+            continue
+        tensors[name] = new.to(kind)
+    write_file(folder / "model.safetensors", tensors)
+    return folder

@@ -166,6 +166,11 @@ def main() -> int:
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
+    parser.add_argument("--design", default=None, choices=["doderax"],
+                        help="instead of the headline workload: prefill and decode throughput of this design at layer "
+                             "sizes that resemble a real model's, beside the dense SwiGLU decoder of equal size, and its "
+                             "kernels alone with their roofline fractions (bench_designs.py)")
+    parser.add_argument("--design-sizes", default="all", help="with --design: w2048, w4096 or all")
     parser.add_argument("--library-modes", default="", help="few-rows epilogues (store,accum,f32,swiglu) to run "
                         "through the library product instead (an experiment switch)")
     parser.add_argument("--pdl", type=int, default=None, choices=[0, 1, 2],
@@ -219,6 +224,14 @@ def main() -> int:
         lib.mir_decode_attention_set_deep_ring_ctas.restype = None
         lib.mir_decode_attention_set_deep_ring_ctas(args.deep_ring_ctas)
     peaks, peaks_kind = read_peaks()
+    if args.design:
+        import bench_designs
+        with ClockSampler() as clocks:
+            report = bench_designs.run(args, peaks)
+        print(json.dumps({"metric": f"{args.design} beside the dense SwiGLU decoder", "unit": "tokens/s, ms, us",
+                          "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                          "peaks": {**peaks, "kind": peaks_kind}, "clocks": clocks.summary(), "report": report}))
+        return 0
     sizes_name, sizes_config = SIZES[args.sizes]
     config = dict(sizes_config)
     layers_full = config["num_hidden_layers"]

@@ -234,7 +234,8 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ positions, int page_size, int heads, int kv_heads, float scale_log2,
                         int window, int partition, int num_partitions, int part_slow, float* __restrict__ partial_o,
-                        float* __restrict__ partial_ml, bf16* __restrict__ out) {
+                        float* __restrict__ partial_ml, bf16* __restrict__ out, int keep_first,
+                        int* __restrict__ virtual_positions) {
   constexpr int STRIDE = D + 8;
   constexpr int TILE_ELEMS = kDecodeTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -254,13 +255,34 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   // writes the newest key and value and rotates q) still runs.  Positions and block tables are older than that
   // kernel, and so is every key but the newest: the first copies of old keys start before the wait.
   const int position = positions[row];
-  if (position < 0) return;                                   // padding row of a captured batch
+  if (position < 0) {                                         // padding row of a captured batch
+    if (keep_first > 0 && window > 0 && virtual_positions && part == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+      virtual_positions[row] = -1;
+    return;
+  }
   const int context = position + 1;
   const int first_key = (window > 0 && context > window) ? context - window : 0;
+  // With a window and kept first keys (keep_first > 0) the CTAs walk over a request's visible keys in a numbering
+  // of their own: the tiles of the kept keys that lie before the window's first tile come first (numbers 0 ..
+  // kept_tiles_end - 1, the same as their true numbers), the window's tiles follow without a gap: number n >=
+  // kept_tiles_end is the true key n + shift.  Partitions, the merge and the newest key's place are counted in these
+  // numbers (the merge gets each row's last number through virtual_positions and no window).  Without kept keys
+  // shift and kept_tiles_end are 0 and a number is the true key.
+  const int first_tile = first_key / kDecodeTile * kDecodeTile;
+  const int kept_end = (keep_first > 0 && window > 0) ? min(keep_first, first_tile) : 0;
+  const int kept_tiles_end = (kept_end + kDecodeTile - 1) / kDecodeTile * kDecodeTile;
+  const bool renumbered = keep_first > 0 && window > 0;
+  const int shift = renumbered ? first_tile - kept_tiles_end : 0;
+  const int numbered_context = context - shift;
+  if (renumbered && virtual_positions && part == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+    virtual_positions[row] = numbered_context - 1;
   const int part_begin = part * partition;
-  const int part_end = min(context, part_begin + partition);
-  const int begin = max(part_begin, first_key / kDecodeTile * kDecodeTile);
+  const int part_end = min(numbered_context, part_begin + partition);
+  const int begin = renumbered ? part_begin : max(part_begin, first_tile);
   if (begin >= part_end) return;                              // the merge skips this partition the same way
+  // the true first key of the tile numbered n, and the first true key beyond what may be read of it
+  auto true_key = [&](int n) { return n < kept_tiles_end ? n : n + shift; };
+  auto true_limit = [&](int n) { return n < kept_tiles_end ? kept_end : min(context, part_end + shift); };
 
   // this warp's buffers: [stage][K | V][16 rows][STRIDE]
   bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * kDecodeStages * 2 * TILE_ELEMS;
@@ -271,14 +293,14 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
 
   // the first copies are on their way before anything else is done; if one of them covers the newest key, the
   // kernel that writes it has to be over first
-  const bool early = my_begin + (kDecodeStages - 2) * stride_keys + kDecodeTile <= position;
+  const bool early = my_begin + (kDecodeStages - 2) * stride_keys + kDecodeTile <= position - shift;
   if (!early) grid_dependency_wait();
 #pragma unroll
   for (int j = 0; j < kDecodeStages - 1; ++j) {
     if (j < my_tiles) {
       bf16* dst = stage_base + j * 2 * TILE_ELEMS;
       load_tile<D, kDecodeTile, 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
-                                    my_begin + j * stride_keys, part_end, lane);
+                                    true_key(my_begin + j * stride_keys), true_limit(my_begin + j * stride_keys), lane);
     }
     cp_async_commit();
   }
@@ -311,23 +333,32 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     if (j + kAhead < my_tiles) {
       bf16* dst = stage_base + ((j + kAhead) % kDecodeStages) * 2 * TILE_ELEMS;
       load_tile<D, kDecodeTile, 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
-                                    my_begin + (j + kAhead) * stride_keys, part_end, lane);
+                                    true_key(my_begin + (j + kAhead) * stride_keys),
+                                    true_limit(my_begin + (j + kAhead) * stride_keys), lane);
     }
     cp_async_commit();
     cp_async_wait<kDecodeStages - 1>();
     __syncwarp();
-    const int tile = my_begin + j * stride_keys;
+    const int tile = true_key(my_begin + j * stride_keys);     // true keys from here on
+    const bool kept_tile = my_begin + j * stride_keys < kept_tiles_end;
     const bf16* k_tile = stage_base + (j % kDecodeStages) * 2 * TILE_ELEMS;
     const bf16* v_tile = k_tile + TILE_ELEMS;
     float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
     scores<D, 2>(s, qa, k_tile, lane);
     float v00 = s[0][0] * scale_log2, v01 = s[0][1] * scale_log2, v10 = s[1][0] * scale_log2, v11 = s[1][1] * scale_log2;
-    if (tile + kDecodeTile > context || tile < first_key) {     // only the edge tiles need a mask
+    if (kept_tile) {                                            // of a kept tile, the kept keys are seen
       const int key = tile + quad * 2;
-      if (key < first_key || key > position) v00 = -INFINITY;
-      if (key + 1 < first_key || key + 1 > position) v01 = -INFINITY;
-      if (key + 8 < first_key || key + 8 > position) v10 = -INFINITY;
-      if (key + 9 < first_key || key + 9 > position) v11 = -INFINITY;
+      if (key >= kept_end) v00 = -INFINITY;
+      if (key + 1 >= kept_end) v01 = -INFINITY;
+      if (key + 8 >= kept_end) v10 = -INFINITY;
+      if (key + 9 >= kept_end) v11 = -INFINITY;
+    } else if (tile + kDecodeTile > context || tile < first_key) {     // only the edge tiles need a mask
+      const int key = tile + quad * 2;
+      const int low = renumbered ? min(first_key, keep_first) : 0;   // (kept keys inside the window's first tile stay)
+      if ((key < first_key && key >= low) || key > position) v00 = -INFINITY;
+      if ((key + 1 < first_key && key + 1 >= low) || key + 1 > position) v01 = -INFINITY;
+      if ((key + 8 < first_key && key + 8 >= low) || key + 8 > position) v10 = -INFINITY;
+      if ((key + 9 < first_key && key + 9 >= low) || key + 9 > position) v11 = -INFINITY;
     }
     const float tile_max = quad_max(fmaxf(fmaxf(v00, v01), fmaxf(v10, v11)));
     const float next = fmaxf(m, tile_max);
@@ -663,8 +694,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
     const bf16* k_tile = buffers + stage * 2 * TILE_ELEMS;
     const bf16* v_tile = k_tile + TILE_ELEMS;
     // this warp needs the tile only if some key of it is visible to some of its rows
-    if (kept_tile || (key0 <= warp_last && key0 + kKeyTile > warp_first_key)) {
-      const bool needs_mask = kept_tile || key0 + kKeyTile - 1 > warp_first ||
+    // (a tile of the window's run may also hold kept keys that lie before this warp's own windows)
+    const bool holds_kept = kept_tile || (window > 0 && key0 < keep_first);
+    if (holds_kept || (key0 <= warp_last && key0 + kKeyTile > warp_first_key)) {
+      const bool needs_mask = holds_kept || key0 + kKeyTile - 1 > warp_first ||
                               (window > 0 && key0 < warp_last + 1 - window + 15);
       constexpr int NT = kKeyTile / 8;
       float s[NT][4];
@@ -731,7 +764,8 @@ template <int D, int STAGES>
 int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                          const int* block_table, int table_width, const int* positions, int rows, int page_size,
                          int heads, int kv_heads, float scale, int window, int partition, int num_partitions,
-                         float* partial_o, float* partial_ml, cudaStream_t stream) {
+                         float* partial_o, float* partial_ml, cudaStream_t stream, int keep_first = 0,
+                         int* virtual_positions = nullptr) {
   const size_t pipeline = (size_t)kDecodeWarps * STAGES * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
   const size_t combine = (size_t)kDecodeWarps * kDecodeHeads * (D + 2) * sizeof(float);
   const size_t smem = pipeline > combine ? pipeline : combine;
@@ -744,8 +778,11 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
   status = mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D, STAGES>, grid,
                            dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
                            table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
-                           partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out);
+                           partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out, keep_first,
+                           virtual_positions);
   if (status != MIR_OK || num_partitions == 1) return status;
+  if (keep_first > 0 && window > 0)      // the partitions were counted in the kernel's own numbering of the visible keys
+    return launch_merge<D>(partial_o, partial_ml, virtual_positions, rows, heads, 0, partition, num_partitions, out, stream);
   return launch_merge<D>(partial_o, partial_ml, positions, rows, heads, window, partition, num_partitions, out, stream);
 }
 
@@ -754,16 +791,16 @@ template <int D>
 int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                   const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
                   int kv_heads, float scale, int window, int partition, int num_partitions, float* partial_o,
-                  float* partial_ml, cudaStream_t stream) {
+                  float* partial_ml, cudaStream_t stream, int keep_first = 0, int* virtual_positions = nullptr) {
   const int group = heads / kv_heads;
   const long long ctas = (long long)num_partitions * kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads) * rows;
   if (ctas <= g_deep_ring_ctas)
     return launch_decode_staged<D, 3>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
                                       page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
-                                      partial_ml, stream);
+                                      partial_ml, stream, keep_first, virtual_positions);
   return launch_decode_staged<D, 2>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
                                     page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
-                                    partial_ml, stream);
+                                    partial_ml, stream, keep_first, virtual_positions);
 }
 
 template <int D>
@@ -860,6 +897,39 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
   return launch_decode<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                             block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
                             partition, num_partitions, partial_o, partial_ml, stream);
+}
+
+// The same with a window's kept first keys (keep_first; virtual_positions: rows ints of scratch for the merge).
+MIR_EXPORT int mir_decode_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                         const void* v_pages, const int* block_table, int table_width,
+                                         const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                         int head_dim, float scale, int window, int partition, int num_partitions,
+                                         float* scratch, long long scratch_floats, cudaStream_t stream, int keep_first, int* virtual_positions) {
+  if (rows == 0) return MIR_OK;
+  if (keep_first < 0 || (keep_first > 0 && window > 0 && virtual_positions == nullptr)) {
+    mir_set_error("decode_attention: kept first keys need room for one number per row");
+    return MIR_BAD_ARGUMENT;
+  }
+  if (bad_common("decode_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
+  if (rows < 0 || rows > 65535 || partition <= 0 || partition % 64 || partition > kDecodeMaxPartition ||
+      num_partitions <= 0 || num_partitions > 65535) {
+    mir_set_error("decode_attention: bad rows %d, partition %d or partition count %d", rows, partition, num_partitions);
+    return MIR_BAD_ARGUMENT;
+  }
+  const long long need = mir_decode_attention_scratch_floats(rows, heads, head_dim, num_partitions);
+  if (need < 0 || (need > 0 && (scratch == nullptr || scratch_floats < need))) {
+    mir_set_error("decode_attention: scratch of %lld floats is needed, got %lld", need, scratch_floats);
+    return MIR_BAD_ARGUMENT;
+  }
+  float* partial_o = scratch;
+  float* partial_ml = scratch ? scratch + (size_t)rows * heads * num_partitions * head_dim : nullptr;
+  if (head_dim == 64)
+    return launch_decode<64>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
+                             block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
+                             partition, num_partitions, partial_o, partial_ml, stream, keep_first, virtual_positions);
+  return launch_decode<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
+                            block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
+                            partition, num_partitions, partial_o, partial_ml, stream, keep_first, virtual_positions);
 }
 
 // Any mix of portions: row r has tokens query_starts[r] .. query_starts[r+1]-1 of the packed batch, and its

@@ -40,9 +40,12 @@ _SIGNATURES = {
         "mir_add_normed_branches": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
         "mir_short_conv_silu": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "mir_delta_rule_scan": [c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_int, c_void_p],
+        "mir_delta_rule_prepare": [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                   c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_delta_rule_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_delta_rule_set_lanes": [c_int],
         "mir_gated_head_norm": [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                 c_int, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
@@ -57,6 +60,9 @@ _SIGNATURES = {
         "mir_decode_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                       c_longlong, c_void_p],
+        "mir_decode_attention_kept_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
+                                           c_longlong, c_void_p, c_int, c_void_p],
         "mir_decode_attention_paged_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                                             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_void_p, c_longlong, c_void_p],
@@ -368,33 +374,80 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, r
                                         positions.data_ptr(), out.data_ptr(), tokens, rows, channels, taps, _stream()))
 
 
-def delta_rule_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, decay_raw: torch.Tensor, dt_bias: torch.Tensor,
-                    a_log: torch.Tensor, state: torch.Tensor, query_starts: torch.Tensor, state_slots: torch.Tensor,
-                    positions: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
-                    value_dim: int, per_channel: bool) -> None:
+def delta_rule_prepare(x: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, beta_raw: torch.Tensor,
+                       decay_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, row_of_token: torch.Tensor,
+                       query_starts: torch.Tensor, state_slots: torch.Tensor, positions: torch.Tensor,
+                       qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, heads: int, kv_heads: int,
+                       key_dim: int, value_dim: int) -> None:
+    """What the gated delta rule needs of every token, in 32-bit: qkv [tokens, 2 kv_heads key_dim + heads value_dim]
+    = silu(short convolution) of the q | k | v columns `x` of the packed projection (as short_conv_silu, with the
+    request's `tail` read and moved on), q and k then unit vectors per head (x / sqrt(sum x^2 + 1e-6)) and q times
+    key_dim^-1/2; beta = sigmoid(beta_raw) [tokens, heads]; decay = exp(-exp(a_log) * softplus(decay_raw + dt_bias))
+    [tokens, heads] or [tokens, heads * key_dim] (one decay per key channel), as wide as decay_raw.  beta_raw and
+    decay_raw are views with unit column stride in x's dtype (decay_raw may be float32)."""
+    _cuda(x, weight, tail, beta_raw, decay_raw, dt_bias, a_log, row_of_token, query_starts, state_slots, positions, qkv,
+          beta, decay)
+    tokens, channels = x.shape
+    taps = weight.shape[1]
+    rows = query_starts.numel() - 1
+    decay_width = decay_raw.shape[1]
+    _require(channels == 2 * kv_heads * key_dim + heads * value_dim and x.stride(1) == 1 and weight.is_contiguous()
+             and weight.shape[0] == channels and weight.dtype == x.dtype and tail.dtype == torch.float32
+             and tail.is_contiguous() and tail.shape[1:] == (max(taps - 1, 0), channels),
+             "delta_rule_prepare: the convolved columns, their weights or their tail do not fit")
+    _require(beta_raw.shape == (tokens, heads) and beta_raw.stride(1) == 1 and beta_raw.dtype == x.dtype
+             and decay_raw.shape[0] == tokens and decay_raw.stride(1) == 1
+             and decay_raw.dtype in (x.dtype, torch.float32) and decay_width in (heads, heads * key_dim)
+             and dt_bias.dtype == torch.float32 and dt_bias.numel() == decay_width and dt_bias.is_contiguous()
+             and a_log.dtype == torch.float32 and a_log.numel() == heads, "delta_rule_prepare: bad gates")
+    for tensor, shape in ((qkv, (tokens, channels)), (beta, (tokens, heads)), (decay, (tokens, decay_width))):
+        _require(tensor.dtype == torch.float32 and tensor.is_contiguous() and tensor.shape == shape,
+                 "delta_rule_prepare: outputs are contiguous float32")
+    _require(all(t.dtype == torch.int32 for t in (row_of_token, query_starts, state_slots, positions)),
+             "delta_rule_prepare: the batch description is int32")
+    lib = library("core")
+    _check(lib, lib.mir_delta_rule_prepare(
+        _is_bf16(x), int(decay_raw.dtype == torch.float32), x.data_ptr(), x.stride(0), weight.data_ptr(), tail.data_ptr(),
+        beta_raw.data_ptr(), beta_raw.stride(0), decay_raw.data_ptr(), decay_raw.stride(0), dt_bias.data_ptr(),
+        a_log.data_ptr(), row_of_token.data_ptr(), query_starts.data_ptr(), state_slots.data_ptr(), positions.data_ptr(),
+        qkv.data_ptr(), beta.data_ptr(), decay.data_ptr(), tokens, rows, heads, kv_heads, key_dim, value_dim, decay_width,
+        taps, _stream()))
+
+
+def delta_rule_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                    query_starts: torch.Tensor, state_slots: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                    heads: int, kv_heads: int, key_dim: int, value_dim: int) -> None:
     """The gated delta rule over the tokens of each request row, from and into state [slots, heads, value_dim,
-    key_dim] (32-bit).  qkv [tokens, 2 kv_heads key_dim + heads value_dim] 32-bit (q | k | v after convolution);
-    beta_raw [tokens, heads] and decay_raw [tokens, heads] or [tokens, heads * key_dim] (one decay per key channel)
-    are views with unit column stride, before sigmoid / softplus; out [tokens, heads * value_dim] 32-bit."""
-    _cuda(qkv, beta_raw, decay_raw, dt_bias, a_log, state, query_starts, state_slots, positions, out)
+    key_dim] (32-bit): per head S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  qkv, beta and
+    decay as delta_rule_prepare leaves them (decay [tokens, heads * key_dim] means one decay per key channel); out
+    [tokens, heads * value_dim] 32-bit."""
+    _cuda(qkv, beta, decay, state, query_starts, state_slots, positions, out)
     tokens = qkv.shape[0]
     rows = query_starts.numel() - 1
-    _require(qkv.dtype == torch.float32 and qkv.is_contiguous()
-             and qkv.shape[1] == 2 * kv_heads * key_dim + heads * value_dim and out.dtype == torch.float32
-             and out.is_contiguous() and out.shape == (tokens, heads * value_dim), "delta_rule_scan: bad qkv or out")
-    _require(beta_raw.shape == (tokens, heads) and beta_raw.stride(1) == 1 and decay_raw.stride(1) == 1
-             and decay_raw.shape == (tokens, heads * key_dim if per_channel else heads)
-             and dt_bias.dtype == torch.float32 and dt_bias.numel() == decay_raw.shape[1] and dt_bias.is_contiguous()
-             and a_log.dtype == torch.float32 and a_log.numel() == heads, "delta_rule_scan: bad gates")
+    per_channel = decay.shape[1] != heads
+    for tensor, shape in ((qkv, (tokens, 2 * kv_heads * key_dim + heads * value_dim)), (beta, (tokens, heads)),
+                          (decay, (tokens, heads * key_dim if per_channel else heads)),
+                          (out, (tokens, heads * value_dim))):
+        _require(tensor.dtype == torch.float32 and tensor.is_contiguous() and tensor.shape == shape,
+                 "delta_rule_scan: qkv, beta, decay and out are contiguous float32 of the stated shapes")
     _require(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, value_dim, key_dim),
              "delta_rule_scan: the state is float32 [slots, heads, value_dim, key_dim]")
-    _require(decay_raw.dtype in (beta_raw.dtype, torch.float32), "delta_rule_scan: bad decay dtype")
     lib = library("core")
-    _check(lib, lib.mir_delta_rule_scan(_is_bf16(beta_raw), int(decay_raw.dtype == torch.float32), int(per_channel),
-                                        qkv.data_ptr(), beta_raw.data_ptr(), beta_raw.stride(0), decay_raw.data_ptr(),
-                                        decay_raw.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(),
-                                        query_starts.data_ptr(), state_slots.data_ptr(), positions.data_ptr(),
-                                        out.data_ptr(), rows, heads, kv_heads, key_dim, value_dim, _stream()))
+    _check(lib, lib.mir_delta_rule_scan(int(per_channel), qkv.data_ptr(), beta.data_ptr(), decay.data_ptr(),
+                                        state.data_ptr(), query_starts.data_ptr(), state_slots.data_ptr(),
+                                        positions.data_ptr(), out.data_ptr(), tokens, rows, heads, kv_heads, key_dim,
+                                        value_dim, _stream()))
+
+
+def set_delta_rule_lanes(lanes: int) -> None:
+    """For measurements: how many lanes share one column of the delta rule's state (8, 16 or 32; 0: the launcher's
+    own choice)."""
+    for name in _LIBS or {"core": None}:
+        lib = library(name)
+        if hasattr(lib, "mir_delta_rule_set_lanes"):
+            lib.mir_delta_rule_set_lanes.argtypes = [c_int]
+            lib.mir_delta_rule_set_lanes.restype = c_int
+            _check(lib, lib.mir_delta_rule_set_lanes(int(lanes)))
 
 
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int,
@@ -566,11 +619,22 @@ def decode_attention_scratch_floats(rows: int, heads: int, head_dim: int, num_pa
     return 0 if num_partitions <= 1 else rows * heads * num_partitions * (head_dim + 2)
 
 
+def decode_attention_kept_plan(rows: int, heads: int, head_dim: int, max_context: int) -> tuple:
+    """(keys per partition, partitions, floats of scratch) for decode_attention with kept first keys, which runs the
+    mma.sync kernel with partitions of decode_partition_keys."""
+    partition = get_option("decode_partition_keys")
+    count = max(1, -(-max_context // partition))
+    return partition, count, decode_attention_scratch_floats(rows, heads, head_dim, count)
+
+
 def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                      block_table: torch.Tensor, positions: torch.Tensor, page_size: int, heads: int, kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], partition: int, num_partitions: int,
-                     scratch: Optional[torch.Tensor]) -> None:
-    """bf16 split-KV attention for a batch of single tokens (row r of qkv belongs to request row r)."""
+                     scratch: Optional[torch.Tensor], keep_first: int = 0,
+                     numbering: Optional[torch.Tensor] = None) -> None:
+    """bf16 split-KV attention for a batch of single tokens (row r of qkv belongs to request row r).  `keep_first`:
+    with a window, the request's first keys that stay visible; the mma.sync kernel then walks over the kept keys and
+    the window's as one run, and `numbering` (int32 [rows]) is scratch for the merge."""
     _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch)
     rows = out.shape[0]
     _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
@@ -582,6 +646,16 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
     lib = library("bf16")
     _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[0] == v_pages.shape[0],
              "decode_attention: the cache tensors must be contiguous [token rows, kv_heads, head_dim]")
+    if keep_first and window:
+        _cuda(numbering)
+        _require(numbering is not None and numbering.dtype == torch.int32 and numbering.numel() >= rows,
+                 "decode_attention: kept first keys need int32 scratch of one number per row")
+        _check(lib, lib.mir_decode_attention_kept_bf16(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+            block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads,
+            head_dim, scale, int(window), partition, num_partitions, _ptr(scratch),
+            0 if scratch is None else scratch.numel(), _stream(), int(keep_first), numbering.data_ptr()))
+        return
     _check(lib, lib.mir_decode_attention_paged_bf16(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
         block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads, head_dim,

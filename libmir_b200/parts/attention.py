@@ -141,11 +141,22 @@ class SoftmaxAttention(Mixer):
         kept = s.keep_first if s.window is not None else 0
         fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
         if fast and kept:
-            # kept first keys: the mma.sync tile kernel walks the kept tiles, then the window's, for every row of the
-            # batch (a decoded token is a portion of one token); the split-key decode kernels do not know kept keys
-            kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.query_starts,
-                                      ctx.context_lens, cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale,
-                                      s.window, tensor_cores=False, keep_first=kept)
+            # kept first keys run the mma.sync kernels, which walk the kept keys and then the window's: single tokens
+            # split over the keys, portions as tiles of queries (the tcgen05 kernels do not know kept keys)
+            singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
+            if singles:
+                longest = ctx.max_context if ctx.decode_only else ctx.single_context
+                partition, count, floats = kernels.decode_attention_kept_plan(singles, s.heads, s.head_dim, longest)
+                scratch = ctx.alloc((floats,), torch.float32) if floats else None
+                kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
+                                         group.block_table[:singles], ctx.positions, cache.page_size, s.heads,
+                                         s.kv_heads, s.head_dim, s.scale, s.window, partition, count, scratch,
+                                         keep_first=kept, numbering=ctx.alloc((singles,), torch.int32))
+            if singles < ctx.num_rows:
+                kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
+                                          ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
+                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window, tensor_cores=False,
+                                          portion_tokens=out.shape[0] - singles, keep_first=kept)
             return
         if fast:
             # the single-token rows come first in the batch: they run as decoded tokens (keys split over CTAs, the

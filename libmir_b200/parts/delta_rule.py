@@ -125,9 +125,6 @@ class GatedDeltaRule(Mixer):
         packed = ctx.alloc((tokens, self.packed_width), self.env.dtype)
         kernels.linear(x, self.w_in, packed, alloc=ctx.alloc)
         segment = lambda name, width=None: packed[:, self.segments[name][0]:self.segments[name][0] + (width or self.segments[name][1])]
-        convolved = ctx.alloc((tokens, self.conv_channels), torch.float32)
-        kernels.short_conv_silu(packed[:, :self.conv_channels], self.w_conv, tail, ctx.row_of_token, ctx.query_starts,
-                                ctx.state_slots, ctx.positions, convolved)
         if s.decay == "channel":
             decay = ctx.alloc((tokens, self.decay_width), torch.float32)           # 32-bit: it enters the recurrence
             kernels.linear(segment("a1", self.w_a2.shape[1]), self.w_a2, decay, alloc=ctx.alloc)
@@ -138,10 +135,16 @@ class GatedDeltaRule(Mixer):
             kernels.linear(segment("g1", self.w_g2.shape[1]), self.w_g2, gate, alloc=ctx.alloc)
         else:
             gate = segment("g")
+        # all tokens in parallel: convolutions, unit vectors, sigmoid and the decays; then the recurrence
+        prepared = ctx.alloc((tokens, self.conv_channels), torch.float32)
+        beta = ctx.alloc((tokens, s.heads), torch.float32)
+        decays = ctx.alloc((tokens, self.decay_width), torch.float32)
+        kernels.delta_rule_prepare(packed[:, :self.conv_channels], self.w_conv, tail, segment("b"), decay, self.dt_bias,
+                                   self.a_log, ctx.row_of_token, ctx.query_starts, ctx.state_slots, ctx.positions,
+                                   prepared, beta, decays, s.heads, s.kv_heads, s.key_dim, s.value_dim)
         read = ctx.alloc((tokens, self.v_width), torch.float32)
-        kernels.delta_rule_scan(convolved, segment("b"), decay, self.dt_bias, self.a_log, state, ctx.query_starts,
-                                ctx.state_slots, ctx.positions, read, s.heads, s.kv_heads, s.key_dim, s.value_dim,
-                                per_channel=s.decay == "channel")
+        kernels.delta_rule_scan(prepared, beta, decays, state, ctx.query_starts, ctx.state_slots, ctx.positions, read,
+                                s.heads, s.kv_heads, s.key_dim, s.value_dim)
         mixed = ctx.alloc((tokens, self.v_width), self.env.dtype)
         kernels.gated_head_norm(read, gate, self.norm, mixed, s.heads, s.value_dim, s.norm_eps, s.gate == "sigmoid")
         if overwrite:

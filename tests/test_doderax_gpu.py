@@ -30,6 +30,22 @@ def close(got, want, tol, what=""):
     assert math.isfinite(error) and error <= bound, f"{what}: max |diff| {error:.3e} > {bound:.3e}"
 
 
+def close_logits(got, want, dtype, what=""):
+    """Logits [positions, vocab] of a whole model.  float32: every value within the tolerance.  bfloat16: the
+    projections are rounded to 8 bits of mantissa, and where a recurrent head reads almost nothing out of its state
+    (a query nearly orthogonal to the few keys written so far, at a request's first tokens) the per-head norm that
+    follows magnifies that rounding to several per cent of the logits at that one position; so positions are judged
+    by their relative root-mean-square error: nine in ten within the tolerance, none beyond five times it.  A lost
+    state, a tap from the wrong token or a window one token off is an error of order one at most positions."""
+    if dtype == "float32":
+        return close(got, want, TOL[dtype], what)
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    relative = np.sqrt(((got - want) ** 2).mean(-1)) / np.sqrt((want ** 2).mean(-1))
+    assert np.isfinite(relative).all(), f"{what}: not finite"
+    assert np.quantile(relative, 0.9) <= TOL[dtype] and relative.max() <= 5 * TOL[dtype], \
+        f"{what}: relative error of positions: 90% {np.quantile(relative, 0.9):.3e}, max {relative.max():.3e}"
+
+
 def batch_description(portions, slots):
     """Device tensors describing packed rows: portions = tokens per request row."""
     starts = np.concatenate([[0], np.cumsum(portions)]).astype(np.int32)
@@ -109,10 +125,12 @@ def test_short_convolution_carries_its_last_inputs_between_portions(dtype, taps)
 
 
 @pytest.mark.parametrize("per_channel", [False, True])
-@pytest.mark.parametrize("heads,kv_heads,key_dim,value_dim", [(2, 2, 64, 32), (6, 2, 24, 40), (1, 1, 200, 3),
-                                                                (4, 1, 96, 128), (3, 3, 8, 1)])
-def test_delta_rule_scan_against_the_plain_recurrence(per_channel, heads, kv_heads, key_dim, value_dim):
-    """Whole sequences and the same cut into portions with the state carried; two requests in one batch."""
+@pytest.mark.parametrize("heads,kv_heads,key_dim,value_dim,taps", [(2, 2, 64, 32, 4), (6, 2, 24, 40, 1), (1, 1, 200, 3, 2),
+                                                                     (4, 1, 96, 128, 3), (3, 3, 8, 1, 1), (2, 1, 30, 5, 4),
+                                                                     (2, 2, 128, 9, 2), (1, 1, 1, 4, 3)])
+def test_delta_rule_against_the_plain_recurrence(per_channel, heads, kv_heads, key_dim, value_dim, taps):
+    """The parallel pass (convolution, unit vectors, gates) and the recurrence: whole sequences, and the same cut into
+    portions with state and convolution tail carried; two requests in one batch beside a slot of somebody else."""
     from libmir_b200 import kernels
     generator = torch.Generator().manual_seed(heads * 100 + key_dim)
     lengths = [40, 29]
@@ -120,30 +138,40 @@ def test_delta_rule_scan_against_the_plain_recurrence(per_channel, heads, kv_hea
     decay_width = heads * key_dim if per_channel else heads
     a_log = torch.rand(heads, generator=generator) * 2 - 1.5
     dt_bias = torch.randn(decay_width, generator=generator)
+    conv = torch.randn(width, taps, generator=generator) * 0.8
     data, want = [], []
     for n in lengths:
-        qkv = torch.randn(n, width, generator=generator)
+        x = torch.randn(n, width, generator=generator)
         beta_raw = torch.randn(n, heads, generator=generator) * 2
         decay_raw = torch.randn(n, decay_width, generator=generator) * 2
-        data.append((qkv, beta_raw, decay_raw))
-        q = qkv[:, :kv_heads * key_dim].reshape(n, kv_heads, key_dim).double()
-        k = qkv[:, kv_heads * key_dim:2 * kv_heads * key_dim].reshape(n, kv_heads, key_dim).double()
-        v = qkv[:, 2 * kv_heads * key_dim:].reshape(n, heads, value_dim).double()
+        data.append((x, beta_raw, decay_raw))
+        mixed = plain.short_conv_silu(x.double(), conv.double())
+        q = mixed[:, :kv_heads * key_dim].reshape(n, kv_heads, key_dim)
+        k = mixed[:, kv_heads * key_dim:2 * kv_heads * key_dim].reshape(n, kv_heads, key_dim)
+        v = mixed[:, 2 * kv_heads * key_dim:].reshape(n, heads, value_dim)
         raw = (decay_raw.double() + dt_bias.double())
         decay = torch.exp(-torch.exp(a_log.double())[None, :, None] * plain.softplus(raw).reshape(n, heads, -1))
         decay = decay.expand(n, heads, key_dim)
         want.append(plain.delta_rule(q, k, v, torch.sigmoid(beta_raw.double()), decay).reshape(n, heads * value_dim))
     for cuts in ([lengths], [[1, 1], [2, 1], [5, 2], [1, 7], [31, 18]]):
         state = torch.zeros(4, heads, value_dim, key_dim, dtype=torch.float32, device=device())
+        tail = torch.zeros(4, taps - 1, width, dtype=torch.float32, device=device())
         state[2] = 7.0                                           # a slot of somebody else
         got, cursors = [[], []], [0, 0]
         for portions in cuts:
             pieces = [[d[r][cursors[r]:cursors[r] + portions[r]] for r in range(2)] for d in zip(*data)]
-            qkv, beta_raw, decay_raw = (torch.cat(piece).contiguous().to(device()) for piece in pieces)
-            _, starts, slots, positions = batch_description(portions, [3, 1])
-            out = torch.empty(sum(portions), heads * value_dim, dtype=torch.float32, device=device())
-            kernels.delta_rule_scan(qkv, beta_raw, decay_raw, dt_bias.to(device()), a_log.to(device()), state, starts,
-                                    slots, positions, out, heads, kv_heads, key_dim, value_dim, per_channel)
+            x, beta_raw, decay_raw = (torch.cat(piece).contiguous().to(device()) for piece in pieces)
+            row_of_token, starts, slots, positions = batch_description(portions, [3, 1])
+            tokens = sum(portions)
+            prepared = torch.empty(tokens, width, dtype=torch.float32, device=device())
+            beta = torch.empty(tokens, heads, dtype=torch.float32, device=device())
+            decay = torch.empty(tokens, decay_width, dtype=torch.float32, device=device())
+            kernels.delta_rule_prepare(x, conv.to(device()), tail, beta_raw, decay_raw, dt_bias.to(device()),
+                                       a_log.to(device()), row_of_token, starts, slots, positions, prepared, beta, decay,
+                                       heads, kv_heads, key_dim, value_dim)
+            out = torch.empty(tokens, heads * value_dim, dtype=torch.float32, device=device())
+            kernels.delta_rule_scan(prepared, beta, decay, state, starts, slots, positions, out, heads, kv_heads,
+                                    key_dim, value_dim)
             at = 0
             for r, count in enumerate(portions):
                 got[r].append(out[at:at + count].cpu())
@@ -151,7 +179,7 @@ def test_delta_rule_scan_against_the_plain_recurrence(per_channel, heads, kv_hea
                 at += count
         for r in range(2):
             close(torch.cat(got[r]), want[r], 2e-5, f"delta rule, request {r}, cuts {len(cuts)}")
-        assert torch.all(state[2] == 7.0) and torch.all(state[0] == 0.0)
+        assert torch.all(state[2] == 7.0) and torch.all(state[0] == 0.0) and torch.all(tail[0] == 0.0)
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])
@@ -276,6 +304,62 @@ def test_tile_attention_with_kept_first_keys(head_dim, page_size, window, keep_f
               f"request {r} head {head} (window {window}, kept {keep_first}, page {page_size})")
 
 
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("page_size,window,keep_first", [(16, 70, 5), (8, 40, 66), (16, 256, 16), (32, 100, 130), (16, 30, 1),
+                                                         (16, 600, 7)])
+def test_split_key_decode_attention_with_kept_first_keys(head_dim, page_size, window, keep_first):
+    """Single decoded tokens of requests that hold 1 to 1,000 keys, split over partitions of 256 keys (bfloat16,
+    mma.sync): each query looks at one key at an edge of its window or of the kept keys."""
+    from libmir_b200 import kernels
+    generator = torch.Generator().manual_seed(window * 7 + keep_first)
+    heads, kv_heads = 6, 2
+    lengths = [1000, 300, window + keep_first + 1, keep_first, 1, 71, 513]
+    lengths = [max(1, n) for n in lengths]
+    dtype = torch.bfloat16
+    pages_each = [-(-n // page_size) for n in lengths]
+    order = torch.randperm(sum(pages_each) + 4, generator=generator)
+    k_pages = torch.full(((sum(pages_each) + 4) * page_size, kv_heads, head_dim), 30.0)
+    v_pages = torch.full(((sum(pages_each) + 4) * page_size, kv_heads, head_dim), -30.0)
+    table = torch.full((len(lengths), max(pages_each)), -1, dtype=torch.int32)
+    queries, want, at = [], [], 0
+    for r, n in enumerate(lengths):
+        table[r, :pages_each[r]] = order[at:at + pages_each[r]].to(torch.int32)
+        at += pages_each[r]
+        k = (torch.randn(n, kv_heads, head_dim, generator=generator) * 0.1).to(dtype)
+        v = torch.randn(n, kv_heads, head_dim, generator=generator).to(dtype)
+        for position in range(n):
+            slot = int(table[r, position // page_size]) * page_size + position % page_size
+            k_pages[slot], v_pages[slot] = k[position].float(), v[position].float()
+        position = n - 1
+        choices = [t for t in (position - window + 1, position - window, keep_first - 1, keep_first, position)
+                   if 0 <= t <= position]
+        q = torch.zeros(heads, head_dim)
+        for head in range(heads):
+            target = choices[(r + head) % len(choices)]
+            q[head] = k[target, head // 3].float() * (600.0 / (head_dim / 16))
+        q = q.to(dtype)
+        mask = plain.visible(n, window, keep_first)[position]
+        rows = []
+        for head in range(heads):
+            scores = (k[:, head // 3].double() @ q[head].double()).masked_fill(~mask, -math.inf)
+            rows.append(torch.softmax(scores, dim=-1) @ v[:, head // 3].double())
+        want.append(torch.cat(rows))
+        queries.append(q.reshape(heads * head_dim))
+    rows = len(lengths)
+    packed = torch.stack(queries).to(device())
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=device())
+    out = torch.empty(rows, heads * head_dim, dtype=dtype, device=device())
+    partition, count, floats = kernels.decode_attention_kept_plan(rows, heads, head_dim, max(lengths))
+    assert count > 1
+    scratch = torch.empty(floats, dtype=torch.float32, device=device())
+    numbering = torch.empty(rows, dtype=torch.int32, device=device())
+    kernels.decode_attention(packed, out, k_pages.to(dtype).to(device()), v_pages.to(dtype).to(device()),
+                             table.contiguous().to(device()), positions, page_size, heads, kv_heads, head_dim, 1.0, window,
+                             partition, count, scratch, keep_first=keep_first, numbering=numbering)
+    for r in range(rows):
+        close(out[r], want[r], 2e-2, f"request of {lengths[r]} keys (window {window}, kept {keep_first}, page {page_size})")
+
+
 # ------------------------------------------------------------------------------ whole models through the engine
 def load(folder, dtype, page_size, pages, requests=4, graphs=False):
     from libmir_b200 import CacheConfig, CudaConfig, Library, RuntimeConfig, SchedulerConfig
@@ -316,15 +400,14 @@ def test_whole_prompts_token_by_token_and_portions(tmp_path, name, dtype):
     ids = random_ids(rng, config["vocab"], 150)
     want = reference(folder, ids)
     model = load(folder, dtype, PAGE_SIZES[name], 40)
-    tol = TOL[dtype]
     whole = feed(model, "whole", ids, [len(ids)])
-    close(whole, want, tol, f"{name}/{dtype} whole")
+    close_logits(whole, want, dtype, f"{name}/{dtype} whole")
     single = feed(model, "single", ids, [1])
-    close(single, want, tol, f"{name}/{dtype} token by token")
+    close_logits(single, want, dtype, f"{name}/{dtype} token by token")
     portions = feed(model, "portions", ids, [2, 3, 1, 7, 2, 16, 5, 2, 33, 1, 2, 9])
-    close(portions, want, tol, f"{name}/{dtype} portions")
+    close_logits(portions, want, dtype, f"{name}/{dtype} portions")
     late = feed(model, "late", ids, [118, 1])                      # most of it whole, the last 32 one by one
-    close(late, want, tol, f"{name}/{dtype} prompt then decoding")
+    close_logits(late, want, dtype, f"{name}/{dtype} prompt then decoding")
     if dtype == "float32":
         # 32-bit results do not depend on the cut at all: the recurrence walks a request's tokens in order, attention
         # reduces a query's keys in an order that depends on its position alone, products reduce in ascending order
@@ -334,7 +417,7 @@ def test_whole_prompts_token_by_token_and_portions(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["X", "Z"])
+@pytest.mark.parametrize("name", ["W", "X", "Z"])
 def test_batches_of_unequal_requests_with_pages_and_slots_that_change_hands(tmp_path, name, dtype):
     """Up to three live requests of unequal lengths, portions of some beside single tokens of others, requests that
     sit a step out, in a pool so small that pages and state slots are used again; every request against itself
@@ -377,7 +460,7 @@ def test_batches_of_unequal_requests_with_pages_and_slots_that_change_hands(tmp_
             del live[index]
         model.cache.check()
     for index in range(len(requests)):
-        close(np.concatenate(got[index]), want[index], TOL[dtype], f"{name}/{dtype} request {index} in a mixed batch")
+        close_logits(np.concatenate(got[index]), want[index], dtype, f"{name}/{dtype} request {index} in a mixed batch")
     stats = model.cache_stats()
     assert stats["free_slots"] == 3
     for group in stats["groups"]:

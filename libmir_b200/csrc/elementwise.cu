@@ -86,6 +86,58 @@ __global__ void add_normed_branches_kernel(NormedBranches branches, float* __res
   }
 }
 
+// The same with 16-byte accesses (hidden a multiple of 4, every pointer 16-byte aligned); the second pass finds the
+// rows in L1.
+__global__ void add_normed_branches_vec4_kernel(NormedBranches branches, float* __restrict__ residual, int hidden,
+                                                float eps, float scale) {
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  const int quads = hidden >> 2;
+  float inverse[4];
+  for (int b = 0; b < branches.count; ++b) {
+    const float4* src = reinterpret_cast<const float4*>(branches.rows[b] + (size_t)row * hidden);
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < quads; c += blockDim.x) {
+      const float4 v = src[c];
+      sum = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sum))));
+    }
+    sum = block_sum(sum, scratch);
+    inverse[b] = rsqrtf(sum / (float)hidden + eps);
+  }
+  float4* dst = reinterpret_cast<float4*>(residual + (size_t)row * hidden);
+  for (int c = threadIdx.x; c < quads; c += blockDim.x) {
+    float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int b = 0; b < branches.count; ++b) {
+      const float4 v = reinterpret_cast<const float4*>(branches.rows[b] + (size_t)row * hidden)[c];
+      const float4 w = __ldg(reinterpret_cast<const float4*>(branches.weight[b]) + c);
+      total.x += v.x * inverse[b] * w.x; total.y += v.y * inverse[b] * w.y;
+      total.z += v.z * inverse[b] * w.z; total.w += v.w * inverse[b] * w.w;
+    }
+    float4 r = dst[c];
+    r.x += scale * total.x; r.y += scale * total.y; r.z += scale * total.z; r.w += scale * total.w;
+    dst[c] = r;
+  }
+}
+
+// gelu_tanh on eight bfloat16 values per thread (16-byte accesses).
+__global__ void gelu_tanh_bf16x8_kernel(__nv_bfloat16* __restrict__ x, size_t total8) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total8) return;
+  float z[8];
+  load8(x + index * 8, z);
+  uint4 packed;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = z[2 * i], b = z[2 * i + 1];
+    h[i] = __floats2bfloat162_rn(0.5f * a * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * a * a, a, a))),
+                                 0.5f * b * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * b * b, b, b))));
+  }
+  *reinterpret_cast<uint4*>(x + index * 8) = packed;
+}
+
 // y[r, :] = x[src(r), :] * rsqrt(mean(x^2) + eps) * w, src(r) = rows ? rows[r] : r.
 // Sum of squares and scaling in 32-bit with a fixed reduction tree.
 template <typename Tout>
@@ -222,7 +274,8 @@ MIR_EXPORT int mir_embed_pairs(int bf16, const void* table, const void* pairs, c
 }
 
 MIR_EXPORT int mir_gelu_tanh(int bf16, void* x, size_t total, cudaStream_t stream) {
-  if (bf16) LAUNCH_1D(gelu_tanh_kernel, total, (__nv_bfloat16*)x, total);
+  if (bf16 && total % 8 == 0 && ((uintptr_t)x & 15) == 0) LAUNCH_1D(gelu_tanh_bf16x8_kernel, total / 8, (__nv_bfloat16*)x, total / 8);
+  else if (bf16) LAUNCH_1D(gelu_tanh_kernel, total, (__nv_bfloat16*)x, total);
   else LAUNCH_1D(gelu_tanh_kernel, total, (float*)x, total);
   return mir_check_launch("gelu_tanh");
 }
@@ -236,6 +289,12 @@ MIR_EXPORT int mir_add_normed_branches(const float* const* branch_rows, const fl
   NormedBranches branches = {};
   branches.count = count;
   for (int b = 0; b < count; ++b) { branches.rows[b] = branch_rows[b]; branches.weight[b] = branch_weights[b]; }
+  bool aligned = (hidden & 3) == 0 && ((uintptr_t)residual & 15) == 0;
+  for (int b = 0; b < count; ++b)
+    aligned = aligned && ((uintptr_t)branch_rows[b] & 15) == 0 && ((uintptr_t)branch_weights[b] & 15) == 0;
+  if (aligned)
+    return mir_launch("add_normed_branches", add_normed_branches_vec4_kernel, dim3(rows), dim3(hidden >= 4096 ? 256 : 128),
+                      0, stream, 0, branches, residual, hidden, eps, scale);
   const int threads = hidden >= 2048 ? 512 : 256;
   return mir_launch("add_normed_branches", add_normed_branches_kernel, dim3(rows), dim3(threads), 0, stream, 0, branches,
                     residual, hidden, eps, scale);

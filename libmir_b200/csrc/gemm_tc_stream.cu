@@ -60,6 +60,7 @@ struct StreamNorm {
   float* best_value;         // float32 epilogue (the output head): [m][best_stride] the largest finite result of every
   int* best_index;           //   32 columns (entry 4 x tile + warp) and its column, ties to the lower column; or null
   int best_stride;
+  int activation;            // store epilogue: 0 none, 1 the tanh GELU of the result
 };
 
 // (Shared memory lets three CTAs share an SM; the registers are capped as if six did: 56 instead of up to 95 per
@@ -308,7 +309,13 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
           const float result = value[j] * (token < kNormStatStride ? scale[token] : 1.0f) + extra + old[j];
           if (in_range) {
             if (MODE == STORE) {
-              reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(result);
+              float stored = result;
+              if (norm.activation == 1) {                     // 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+                float t;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * result * result, result, result)));
+                stored = 0.5f * result * (1.0f + t);
+              }
+              reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(stored);
             } else {
               reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = result;
               if (MODE == ACCUM && norm.weighted_out != nullptr)
@@ -439,6 +446,11 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
                                        int sumsq_tiles, float eps, float* sumsq_out, const float* next_weight,
                                        void* weighted_out, int ld_weighted, cudaStream_t stream) {
   if (m == 0 || n == 0) return MIR_OK;
+  const bool gelu = mode == 4;                                 // mode 4: the store epilogue with the tanh GELU, no bias
+  if (gelu) {
+    if (bias) { mir_set_error("tc_stream: the GELU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
+    mode = STORE;
+  }
   if (m < 0 || m > 128 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) || (ldx % 8) || ldx < k ||
       ((uintptr_t)x & 15) || x == nullptr) {
     mir_set_error("tc_stream: needs 1..128 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
@@ -470,6 +482,7 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
   norm.best_value = nullptr;
   norm.best_index = nullptr;
   norm.best_stride = 0;
+  norm.activation = gelu ? 1 : 0;
   switch (mode) {
     case STORE: return launch<STORE>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
     case ACCUM: return launch<ACCUM>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
@@ -510,5 +523,6 @@ MIR_EXPORT int mir_gemm_tc_stream_head_bf16(const void* x, int ldx, const void* 
   norm.best_value = best_value;
   norm.best_index = best_index;
   norm.best_stride = best_stride;
+  norm.activation = 0;
   return launch<F32>(x, ldx, w, nullptr, out, ldo, m, n, k, 0, norm, stream);
 }

@@ -220,6 +220,9 @@ def loaded_libraries() -> dict:
 # leaves the sums of squares and the weighted rows, the product after it scales its results.  Two kernels fewer
 # per layer in a decode step.
 FUSE_NORM_INTO_PRODUCT = True
+# Whether the tanh GELU of a feed-forward runs in the epilogue of the product before it (our tcgen05 kernels) instead
+# of as a kernel of its own after a library product.
+FUSE_GELU_INTO_PRODUCT = True
 # Whether layers of the built-in kind are run by the native executor (csrc/executor.cu), one call per run of such
 # layers; False runs every layer part by part from Python (the same kernels, launched from the interpreter).
 NATIVE_LAYERS = True
@@ -839,6 +842,32 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
     return bool(wrote.value)
 
 
+def linear_gelu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, alloc=None) -> None:
+    """out = gelu_tanh(x . weight^T) in the activations' dtype.  bfloat16: one kernel with the activation in its
+    epilogue where our tcgen05 products take the rows (up to few_rows_max on the weight-streaming kernel, from
+    tensor_core_min_rows on the many-rows kernel; the approximate hardware tanh, whose error is below bfloat16's
+    rounding), else the library product and the activation kernel.  float32: the 32-bit product and that kernel."""
+    _cuda(x, weight, out)
+    m, k = x.shape
+    n = weight.shape[0]
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k % 8 == 0
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.stride(1) == 1 and out.stride(1) == 1
+            and weight.is_contiguous() and out.shape == (m, n) and FUSE_GELU_INTO_PRODUCT):
+        lib = library("bf16")
+        if 0 < m <= min(get_option("few_rows_max"), STREAM_MAX_ROWS):
+            _check(lib, lib.mir_gemm_tc_stream_bf16(MODE_GELU, x.data_ptr(), x.stride(0), weight.data_ptr(), None,
+                                                    out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, 0.0, None, None,
+                                                    None, 0, _stream()))
+            return
+        if m >= get_option("tensor_core_min_rows"):
+            _check(lib, lib.mir_gemm_tc_bf16(MODE_GELU, x.data_ptr(), x.stride(0), weight.data_ptr(), None,
+                                             out.data_ptr(), out.stride(0), m, n, k, 0, _stream()))
+            return
+    linear(x, weight, out, alloc=alloc)
+    _require(out.is_contiguous(), "linear_gelu: a contiguous result is needed")
+    gelu_tanh(out)
+
+
 def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
                        bias: Optional[torch.Tensor] = None, accumulate: bool = False, swiglu: bool = False) -> None:
     """The tcgen05 product for many bfloat16 rows: out = x . weight^T (+ bias) as bfloat16, or as float32
@@ -917,7 +946,7 @@ def tensor_core_linear_error() -> int:
 
 
 NORM_STAT_STRIDE = 32        # tokens per row of the sums-of-squares arrays (kNormStatStride of the kernels)
-MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU = 0, 1, 2, 3
+MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU, MODE_GELU = 0, 1, 2, 3, 4
 
 
 def few_rows_max() -> int:

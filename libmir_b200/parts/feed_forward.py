@@ -47,8 +47,8 @@ class SwiGlu(FeedForward):
 
 
 class GeluMlp(FeedForward):
-    """down(gelu_tanh(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit on the
-    product's rows, in place."""
+    """down(gelu_tanh(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit, in the
+    epilogue of the up projection where our own products run it, else on the product's rows, in place."""
 
     graph_safe = True
 
@@ -70,6 +70,5 @@ class GeluMlp(FeedForward):
 
     def forward(self, ctx, x, residual):
         hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)
-        kernels.linear(x, self.w_up, hidden, alloc=ctx.alloc)
-        kernels.gelu_tanh(hidden)
+        kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc)     # the activation in the product's epilogue
         ctx.accumulate(hidden, self.w_down, residual)

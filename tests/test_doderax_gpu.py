@@ -515,3 +515,19 @@ def test_trace_runner_picks_the_design_by_its_configuration(tmp_path):
         for index, rows in enumerate(trace.expect):
             for row, (name, position) in enumerate(rows):
                 close(results[index][row], want[name][position], TOL[dtype], f"trace {dtype} {name}@{position}")
+
+
+@pytest.mark.parametrize("rows", [1, 8, 32, 33, 127, 128, 300])
+def test_up_projection_with_the_activation_in_its_epilogue(rows):
+    """gelu_tanh(x W^T) in bfloat16 through every product the row count selects (weight streaming, the library with
+    the activation kernel, the many-rows tcgen05 kernel) against float64."""
+    from libmir_b200 import kernels
+    generator = torch.Generator().manual_seed(rows)
+    k, n = 96, 200
+    x = torch.randn(rows, k, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=generator) * 0.3).to(torch.bfloat16)
+    out = torch.empty(rows, n, dtype=torch.bfloat16, device=device())
+    alloc = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=device())
+    kernels.linear_gelu(x.to(device()), w.to(device()), out, alloc=alloc)
+    close(out, plain.gelu_tanh(x.double() @ w.double().T), 1e-2, f"linear_gelu, {rows} rows")
+    assert kernels.stream_linear_error() == 0 and kernels.tensor_core_linear_error() == 0

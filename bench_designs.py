@@ -231,7 +231,7 @@ def run(args, peaks: dict) -> dict:
             window = s["window"]
             scale = dim ** -0.5
             calls = [lambda k=k, v=v: kernels.prefill_attention(qkv, mixed, k, v, block_table, starts, contexts, PAGE, heads,
-                                                                 kv_heads, dim, scale, window, tensor_cores=False,
+                                                                 kv_heads, dim, scale, window,
                                                                  keep_first=s["keep_first"]) for k, v in zip(k_cache, v_cache)]
             if portion > 1:
                 visible = sum(min(p + 1, window) for p in range(PROMPT))

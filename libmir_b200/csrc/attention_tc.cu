@@ -224,15 +224,25 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
 struct Work {
   bool valid;
   int head, kv_head, q_row0, tile_rows, first_position, last_position, first_key, key_begin, key_end, tiles;
+  // A window's kept first keys: if some query of the item has keys [0, kept) outside its window, the item's first
+  // kept_tiles tiles are the key tiles from key 0 on, in which exactly the keys below `kept` are seen (by every
+  // query), and in the window's tiles that follow those keys are hidden, so that no key counts twice.  Else 0, 0.
+  int kept, kept_tiles;
   const int* table;
 };
+
+// The first key of the item's tile t.
+__device__ __forceinline__ int tile_first_key(const Work& w, int t) {
+  return t < w.kept_tiles ? t * kKeys : w.key_begin + (t - w.kept_tiles) * kKeys;
+}
 
 // Item `index` of the launch: head = index % heads (the fast index, so that the heads of a group, which read the
 // same keys, run at the same time), and the batch's `query_tiles` query tiles from the last one of the last row
 // backwards (late tiles see the most keys: they come first).
 __device__ __forceinline__ Work work_item(int index, int items, int query_tiles, int heads, int kv_heads, int num_rows,
                                           const int* __restrict__ query_starts, const int* __restrict__ context_lens,
-                                          const int* __restrict__ block_table, int table_width, int window) {
+                                          const int* __restrict__ block_table, int table_width, int window,
+                                          int keep_first) {
   Work w;
   w.valid = false;
   if (index < 0 || index >= items) return w;
@@ -259,6 +269,10 @@ __device__ __forceinline__ Work work_item(int index, int items, int query_tiles,
   w.key_begin = w.first_key / kKeys * kKeys;
   w.key_end = w.last_position + 1;                            // exclusive
   w.tiles = (w.key_end - w.key_begin + kKeys - 1) / kKeys;
+  const bool some_hidden = window > 0 && keep_first > 0 && w.last_position - window + 1 > 0;
+  w.kept = some_hidden ? min(keep_first, w.key_end) : 0;
+  w.kept_tiles = (w.kept + kKeys - 1) / kKeys;
+  w.tiles += w.kept_tiles;
   w.valid = true;
   return w;
 }
@@ -278,7 +292,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                             const __grid_constant__ CUtensorMap v_tile_map, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                             const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
-                            float scale_log2, int window, int tile_slots) {
+                            float scale_log2, int window, int tile_slots, int keep_first) {
   constexpr int kThreads = threads_for(kStreams);
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
@@ -305,7 +319,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const int items = heads * query_tiles;
   auto work = [&](int k) {
     return work_item(item_of(k, cta, ctas, items), items, query_tiles, heads, kv_heads, num_rows, query_starts,
-                     context_lens, block_table, table_width, window);
+                     context_lens, block_table, table_width, window, keep_first);
   };
   auto more = [&](int k) { return (long long)k * ctas < items; };
 
@@ -378,12 +392,12 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         }
       }
       const int x = w.kv_head * kDim + half * 64;
-      const int lane_key = w.key_begin + slot * page_size;    // the first key of this lane's page in tile 0
-      const int* entry = w.table + (lane_key >> page_shift);  // its block table entry; pages_per_tile further per tile
       const int tiles = w.tiles, key_end = w.key_end, first_visible = w.first_key - page_size;
-      auto page_of = [&](int t) {
-        const int key = lane_key + t * kKeys;
-        return (loads && t < tiles && key < key_end && key > first_visible) ? entry[t * pages_per_tile] : -1;
+      auto page_of = [&](int t) {                              // this lane's page of tile t, -1 if nothing of it is seen
+        if (!loads || t >= tiles) return -1;
+        const int key = tile_first_key(w, t) + slot * page_size;   // the page's first key
+        const bool wanted = t < w.kept_tiles ? key < w.kept : (key < key_end && key > first_visible);
+        return wanted ? w.table[key >> page_shift] : -1;
       };
       // this loader's tiles of the item: every one, or those whose number in the CTA is even (odd)
       const int first_tile = turns == 1 ? 0 : ((g0 & 1) == turn ? 0 : 1);
@@ -534,7 +548,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         const int g = g0 + t;
         const int stage = kShared ? g % 3 : g & 1;            // the score accumulator of the tile
         const uint32_t parity = (uint32_t)(kShared ? g / 3 : g >> 1) & 1u;
-        const int key0 = w.key_begin + t * kKeys;
+        const int key0 = tile_first_key(w, t);
+        const bool kept_tile = t < w.kept_tiles;
         const int stamp_tile = (lane == 0 && quarter == 0 && part == 0) ? g : -1;
         ATT_STAMP(stamp_tile, 5);
         if (alive && !wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; }
@@ -542,9 +557,16 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         tensor_fence_after_sync();
         const uint32_t scores = tmem_base + (uint32_t)stage * 128u + lane_bits;
         // keys of this tile that row r may see: columns [low, high]; most tiles are visible to every row
-        const int high = position - key0;                     // last visible column, may be >= 128 or < 0
-        const int low = window > 0 ? position - window + 1 - key0 : -1;
-        const bool every = key0 + kKeys - 1 <= w.first_position && (window == 0 || w.last_position - window + 1 <= key0);
+        int high = position - key0;                           // last visible column, may be >= 128 or < 0
+        int low = window > 0 ? position - window + 1 - key0 : -1;
+        if (kept_tile) {                                      // of a kept tile the kept keys are seen, by every row
+          high = min(high, w.kept - 1 - key0);
+          low = -1;
+        } else if (w.kept > 0) {                              // (they are hidden where the window's tiles hold them again)
+          low = max(low, w.kept - key0);
+        }
+        const bool every = !kept_tile && key0 >= w.kept && key0 + kKeys - 1 <= w.first_position &&
+                           (window == 0 || w.last_position - window + 1 <= key0);
         uint32_t packed[kCols / 2];
         bool grow;
         float factor;
@@ -711,12 +733,15 @@ MIR_EXPORT int mir_prefill_attention_tc_takes(int head_dim, int page_size) {
 // context_lens[r] cached tokens include them.  q is the packed [tokens, q_stride] buffer whose first
 // heads * 128 columns are the rotated queries; out is [tokens, heads * 128]; k_pages and v_pages are
 // [cache_rows, kv_heads, 128].
-MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                             const void* v_pages, long long cache_rows, const int* block_table,
-                                             int table_width, const int* query_starts, const int* context_lens,
-                                             int num_rows, int tokens, int page_size, int heads, int kv_heads,
-                                             int head_dim, float scale, int window, cudaStream_t stream) {
+// keep_first: with a window, the first keys of every request that stay visible to all its later queries.
+MIR_EXPORT int mir_prefill_attention_tc_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                  const void* v_pages, long long cache_rows, const int* block_table,
+                                                  int table_width, const int* query_starts, const int* context_lens,
+                                                  int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                                  int head_dim, float scale, int window, int keep_first,
+                                                  cudaStream_t stream) {
   if (num_rows == 0 || tokens == 0) return MIR_OK;
+  if (keep_first < 0) { mir_set_error("prefill_attention_tc: keep_first is negative"); return MIR_BAD_ARGUMENT; }
   if (!mir_prefill_attention_tc_takes(head_dim, page_size) || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       table_width <= 0 || window < 0 || num_rows < 0 || tokens < 0 || scale <= 0.0f ||
       (q_stride % 8) || q_stride < (long long)heads * kDim || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) ||
@@ -772,16 +797,26 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
     return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, true>, dim3(ctas), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                      scale * 1.4426950408889634f, window, tile_slots);
+                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0);
   if (g_streams == 2)
     return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, false>, dim3(ctas), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                      scale * 1.4426950408889634f, window, tile_slots);
+                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0);
   return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1, false>, dim3(ctas), dim3(threads_for(1)),
                     (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                    scale * 1.4426950408889634f, window, tile_slots);
+                    scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0);
+}
+
+MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                             const void* v_pages, long long cache_rows, const int* block_table,
+                                             int table_width, const int* query_starts, const int* context_lens,
+                                             int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                             int head_dim, float scale, int window, cudaStream_t stream) {
+  return mir_prefill_attention_tc_kept_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                            query_starts, context_lens, num_rows, tokens, page_size, heads, kv_heads,
+                                            head_dim, scale, window, 0, stream);
 }
 
 // For measurements: 2 (the default) splits a row's key tiles over two softmax streams, 1 runs one stream.

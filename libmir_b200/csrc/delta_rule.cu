@@ -24,7 +24,7 @@ using namespace mir;
 
 namespace {
 
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 16;
 constexpr int kMaxPerLane = 8;          // key channels per lane: key_dim <= 256
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }

@@ -81,6 +81,9 @@ _SIGNATURES = {
         "mir_prefill_attention_tc_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                           c_void_p],
+        "mir_prefill_attention_tc_kept_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                               c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                               c_float, c_int, c_int, c_void_p],
         "mir_prefill_attention_tc_takes": [c_int, c_int],
         "mir_prefill_attention_tc_error": [],
         "mir_prefill_attention_tc_set_streams": [c_int],
@@ -681,7 +684,7 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
     """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]
     of the packed qkv and out; the rows may be a part of the batch, `portion_tokens` then says how many tokens
     they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses.
-    `keep_first`: with a window, the first keys of a request that every later query still sees (mma.sync kernel)."""
+    `keep_first`: with a window, the first keys of a request that every later query still sees."""
     _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens)
     tokens = out.shape[0]
     rows = context_lens.numel()
@@ -693,9 +696,6 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
              and block_table.shape[0] >= rows, "prefill_attention: bad metadata")
     lib = library("bf16")
     keep_first = int(keep_first or 0) if window else 0
-    if keep_first:
-        _require(not tensor_cores, "prefill_attention: kept first keys run the mma.sync kernel")
-        tensor_cores = False
     if tensor_cores is None:
         portion_tokens = tokens if portion_tokens is None else portion_tokens
         tensor_cores = (PREFILL_TENSOR_CORES and portion_tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
@@ -704,10 +704,10 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
     if tensor_cores:
         _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape,
                  "prefill_attention: the tcgen05 kernel reads contiguous [rows, kv_heads, head_dim] pages")
-        _check(lib, lib.mir_prefill_attention_tc_bf16(
+        _check(lib, lib.mir_prefill_attention_tc_kept_bf16(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
             block_table.data_ptr(), block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens,
-            page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream()))
+            page_size, heads, kv_heads, head_dim, scale, int(window or 0), keep_first, _stream()))
         return
     _check(lib, lib.mir_prefill_attention_kept_bf16(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),

@@ -141,8 +141,9 @@ class SoftmaxAttention(Mixer):
         kept = s.keep_first if s.window is not None else 0
         fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
         if fast and kept:
-            # kept first keys run the mma.sync kernels, which walk the kept keys and then the window's: single tokens
-            # split over the keys, portions as tiles of queries (the tcgen05 kernels do not know kept keys)
+            # kept first keys: single tokens run the mma.sync kernel split over the keys, which walks the kept keys
+            # and then the window's (the tcgen05 decode kernel does not know kept keys); portions run as tiles of
+            # queries on either tile kernel
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
             if singles:
                 longest = ctx.max_context if ctx.decode_only else ctx.single_context
@@ -155,7 +156,7 @@ class SoftmaxAttention(Mixer):
             if singles < ctx.num_rows:
                 kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
                                           ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
-                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window, tensor_cores=False,
+                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
                                           portion_tokens=out.shape[0] - singles, keep_first=kept)
             return
         if fast:

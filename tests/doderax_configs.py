@@ -71,8 +71,17 @@ DODERAX_W = {   # key and value heads of 64 and of 128 with kept first tokens: i
     ],
 }
 
-ALL = {"W": DODERAX_W, "X": DODERAX_X, "Y": DODERAX_Y, "Z": DODERAX_Z}
-PAGE_SIZES = {"W": 16, "X": 8, "Y": 16, "Z": 8}
+DODERAX_V = {   # recurrent layers only (no pages at all), a width that is no multiple of 8, seven taps, five heads
+    "architecture": "Doderax", "vocab": 97, "width": 100, "logit_scale": 0.75, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 31, "mul_prev": 1, "mul_cur": 2}},
+    "layers": [
+        _layer("channel_delta", _right(5, 5, 48, 20, 7), 120),
+        _layer("channel_delta", _right(2, 1, 72, 36, 3), 0),
+    ],
+}
+
+ALL = {"V": DODERAX_V, "W": DODERAX_W, "X": DODERAX_X, "Y": DODERAX_Y, "Z": DODERAX_Z}
+PAGE_SIZES = {"V": 16, "W": 16, "X": 8, "Y": 16, "Z": 8}
 
 
 def make_folder(tmp_path, config: dict, seed: int, dtype: str, sharpen: float = 4.0) -> Path:

@@ -534,3 +534,30 @@ def test_up_projection_with_the_activation_in_its_epilogue(rows):
     kernels.linear_gelu(x.to(device()), w.to(device()), out, alloc=alloc)
     close(out, plain.gelu_tanh(x.double() @ w.double().T), 1e-2, f"linear_gelu, {rows} rows")
     assert kernels.stream_linear_error() == 0 and kernels.tensor_core_linear_error() == 0
+
+
+def test_generate_command_line(tmp_path):
+    """bin/generate on a model folder of the design: two prompts as one batch, greedy, against the plain
+    implementation; and one prompt sampled with a seed, twice, for the same tokens."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    config = ALL["X"]
+    folder = make_folder(tmp_path / "model", config, seed=12, dtype="float32")
+    plain_config, weights = plain.read_model(folder)
+    command = [sys.executable, str(ROOT / "bin" / "generate"), str(folder), "--dtype", "float32", "--block-size", "8",
+               "--block-count", "64", "--max-tokens", "6", "--ignore-eos"]
+    done = subprocess.run(command + ["--prompt-ids", "5,9,200,33;7", "--json"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-3000:]
+    outputs = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    assert len(outputs) == 2
+    for prompt, output in zip(([5, 9, 200, 33], [7]), outputs):
+        ids = list(prompt)
+        for token in output["token_ids"]:
+            logits = plain.forward(plain_config, weights, ids)[-1]
+            best = int(torch.argmax(logits))
+            assert token == best or float(logits[best] - logits[token]) < 1e-4
+            ids.append(token)
+    sampled = [subprocess.run(command + ["--prompt-ids", "1,2,3", "--temperature", "0.9", "--top-k", "20", "--seed", "4"],
+                              capture_output=True, text=True, timeout=600).stdout for _ in range(2)]
+    assert sampled[0] == sampled[1] and "finish_reason=" in sampled[0]

@@ -1,5 +1,5 @@
 // Paged grouped-query softmax attention, one code path for portions of prompts and for decoded
-// tokens, any head size that is a multiple of 8 up to 256, any number of heads and groups,
+// tokens, any head size up to 512 (16-byte loads where it is a multiple of 8), any number of heads and groups,
 // optional sliding window, float or bf16 storage.  One warp per (token, query head).
 //
 // This is the reference kernel of the engine: the 32-bit path always runs it, and the bf16 path
@@ -19,7 +19,7 @@
 
 using namespace mir;
 
-constexpr int kMaxHeadDim = 256;
+constexpr int kMaxHeadDim = 512;
 constexpr int kWarpsPerBlock = 4;
 
 template <typename T>
@@ -67,11 +67,15 @@ __global__ void paged_attention_generic_kernel(
       key_offset = ((size_t)page * page_size + key % page_size) * kv_heads + kv_head;
       const T* k_row = k_pages + key_offset * head_dim;
       float dot = 0.0f;
-      for (int d = 0; d < head_dim; d += 8) {
-        float k8[8];
-        load8(k_row + d, k8);
+      if (head_dim % 8 == 0) {                                // (then every key row starts on a 16-byte boundary)
+        for (int d = 0; d < head_dim; d += 8) {
+          float k8[8];
+          load8(k_row + d, k8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dot = fmaf(q_shared[warp][d + i], k8[i], dot);
+          for (int i = 0; i < 8; ++i) dot = fmaf(q_shared[warp][d + i], k8[i], dot);
+        }
+      } else {
+        for (int d = 0; d < head_dim; ++d) dot = fmaf(q_shared[warp][d], to_float(k_row[d]), dot);
       }
       score = dot * scale;
     }
@@ -117,8 +121,8 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
                   heads, kv_heads, page_size, table_width);
     return MIR_BAD_ARGUMENT;
   }
-  if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 8) {
-    mir_set_error("paged_attention: head_dim %d is not a multiple of 8 in [8, %d]", head_dim, kMaxHeadDim);
+  if (head_dim <= 0 || head_dim > kMaxHeadDim) {
+    mir_set_error("paged_attention: head_dim %d is not in [1, %d]", head_dim, kMaxHeadDim);
     return MIR_BAD_ARGUMENT;
   }
   if (value_dim <= 0 || value_dim > kMaxHeadDim) {

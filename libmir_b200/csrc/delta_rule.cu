@@ -240,15 +240,20 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
   copy_commit();
   int stage = 0;
   float pending = 0.0f;                                          // the last token's read-out, not yet summed over the lanes
-  int pending_token = -1;
+  bool has_pending = false;
+  const bool writer = l == 0 && active;
+  const size_t out_step = (size_t)heads * value_dim;
+  float* out_at = out + ((size_t)start * heads + head) * value_dim + (active ? column : 0) - out_step;   // the pending token's place
   for (int from = start; from < end; from += kScanChunk, stage ^= 1) {
     if (from + kScanChunk < end) stage_in(from + kScanChunk, staged + (stage ^ 1) * kScanChunk * ROW);
     copy_commit();
     copy_wait<1>();
     __syncthreads();
     const int count = min(kScanChunk, end - from);
+    const float* in = staged + stage * kScanChunk * ROW - ROW;
+#pragma unroll 2
     for (int t = 0; t < count; ++t) {
-      const float* in = staged + (stage * kScanChunk + t) * ROW;
+      in += ROW;
       const float b = in[2 * PADDED + DECAYS];
       const float v = in[2 * PADDED + DECAYS + 4 + local_column];
       const float head_decay = in[2 * PADDED];
@@ -275,7 +280,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         total += __shfl_xor_sync(0xffffffffu, total, o);
         pending += __shfl_xor_sync(0xffffffffu, pending, o);
       }
-      if (pending_token >= 0 && l == 0 && active) out[((size_t)pending_token * heads + head) * value_dim + column] = pending;
+      if (has_pending && writer) *out_at = pending;
+      out_at += out_step;
       const float update = b * (v - total);
       float read[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -292,7 +298,7 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         read[3] = fmaf(s[m + 3], query.w, read[3]);
       }
       pending = (read[0] + read[1]) + (read[2] + read[3]);
-      pending_token = from + t;
+      has_pending = true;
     }
     __syncthreads();                                              // the stage is free for the chunk after next
   }
@@ -300,7 +306,7 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
 #pragma unroll
   for (int o = LANES / 2; o > 0; o >>= 1) pending += __shfl_xor_sync(0xffffffffu, pending, o);
   if (!active) return;
-  if (l == 0) out[((size_t)pending_token * heads + head) * value_dim + column] = pending;
+  if (l == 0) *out_at = pending;
 #pragma unroll
   for (int m = 0; m < PER; m += 4) {
     const int i = (m / 4 * LANES + l) * 4;

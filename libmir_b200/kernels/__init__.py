@@ -565,7 +565,6 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
     _require(qkv.is_contiguous() and qkv.shape[1] == (heads + kv_heads) * head_dim + kv_heads * value_dim,
              "qk_rope_store: bad qkv")
     _require(positions.dtype == torch.int32 and positions.numel() >= tokens, "qk_rope_store: bad positions")
-    _require(head_dim % 8 == 0, f"qk_rope_store: head_dim {head_dim} is not a multiple of 8")
     if rotary_dim:
         _require(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
                  "qk_rope_store: the angle table must hold rotary_dim / 2 float32 values")

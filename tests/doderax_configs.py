@@ -80,8 +80,17 @@ DODERAX_V = {   # recurrent layers only (no pages at all), a width that is no mu
     ],
 }
 
-ALL = {"V": DODERAX_V, "W": DODERAX_W, "X": DODERAX_X, "Y": DODERAX_Y, "Z": DODERAX_Z}
-PAGE_SIZES = {"V": 16, "W": 16, "X": 8, "Y": 16, "Z": 8}
+DODERAX_U = {   # attention heads whose widths are no multiples of 8 (keys 20, values 12, 6 rotated); a rank of 3
+    "architecture": "Doderax", "vocab": 120, "width": 72, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+    "layers": [
+        _layer("parallel", {"left": _left(4, 2, 20, 12, 0.22, rot=(6, 77.0), mask=(11, 2)),
+                            "right": _right(2, 2, 12, 10, 2)}, 80),
+        _layer("channel_delta", dict(_right(3, 1, 20, 4, 4), decay_rank=3, gate_rank=5), 0),
+    ],
+}
+
+ALL = {"U": DODERAX_U, "V": DODERAX_V, "W": DODERAX_W, "X": DODERAX_X, "Y": DODERAX_Y, "Z": DODERAX_Z}
+PAGE_SIZES = {"U": 4, "V": 16, "W": 16, "X": 8, "Y": 16, "Z": 8}
 
 
 def make_folder(tmp_path, config: dict, seed: int, dtype: str, sharpen: float = 4.0) -> Path:

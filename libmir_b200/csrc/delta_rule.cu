@@ -241,6 +241,26 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
   int stage = 0;
   float pending = 0.0f;                                          // the last token's read-out, not yet summed over the lanes
   bool has_pending = false;
+  __shared__ __align__(16) float exchange[kScanWarps][2][64];   // [warp][token parity][S^T k parts | read-out parts]
+  int parity = 0;
+  auto sum_over_lanes = [&](float& first, float& second) {       // both sums in one fixed order, whichever token it is
+    float* parts = exchange[threadIdx.y][parity];
+    parts[threadIdx.x] = first;
+    parts[32 + threadIdx.x] = second;
+    __syncwarp();
+    const float* mine = parts + (threadIdx.x / LANES) * LANES;
+    float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+    for (int piece = 0; piece < LANES; piece += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(mine + piece);
+      const float4 b = *reinterpret_cast<const float4*>(mine + 32 + piece);
+      sum_a += (a.x + a.y) + (a.z + a.w);
+      sum_b += (b.x + b.y) + (b.z + b.w);
+    }
+    first = sum_a;
+    second = sum_b;
+    parity ^= 1;
+  };
   const bool writer = l == 0 && active;
   const size_t out_step = (size_t)heads * value_dim;
   float* out_at = out + ((size_t)start * heads + head) * value_dim + (active ? column : 0) - out_step;   // the pending token's place
@@ -273,13 +293,12 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         seen[3] = fmaf(s[m + 3], key.w, seen[3]);
       }
       float total = (seen[0] + seen[1]) + (seen[2] + seen[3]);
-      // two sums over the lanes of a column at once: this token's S^T k and the token before's read-out, which is
-      // not on the path to the next state, so its shuffles ride along with these
-#pragma unroll
-      for (int o = LANES / 2; o > 0; o >>= 1) {
-        total += __shfl_xor_sync(0xffffffffu, total, o);
-        pending += __shfl_xor_sync(0xffffffffu, pending, o);
-      }
+      // Two sums over the lanes of a column at once: this token's S^T k and the token before's read-out, which is not
+      // on the path to the next state.  The lanes exchange their parts through shared memory (a store, a warp barrier
+      // and 16-byte loads that every lane of the column adds up in the same order) rather than by shuffles: a chain
+      // of log2(LANES) dependent shuffles costs this lone warp more than the round trip.  Two buffers by the
+      // token's parity: a lane may still read one while the next token's parts are written.
+      sum_over_lanes(total, pending);
       if (has_pending && writer) *out_at = pending;
       out_at += out_step;
       const float update = b * (v - total);
@@ -303,8 +322,10 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     __syncthreads();                                              // the stage is free for the chunk after next
   }
   copy_wait<0>();
-#pragma unroll
-  for (int o = LANES / 2; o > 0; o >>= 1) pending += __shfl_xor_sync(0xffffffffu, pending, o);
+  {
+    float unused = 0.0f;
+    sum_over_lanes(unused, pending);                             // the last token's read-out
+  }
   if (!active) return;
   if (l == 0) *out_at = pending;
 #pragma unroll

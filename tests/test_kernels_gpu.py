@@ -304,13 +304,13 @@ def test_attention_sees_one_far_key_among_hundreds_and_the_windows_edge(dtype):
 
 def test_kernels_refuse_sizes_they_do_not_take():
     from libmir_b200 import KernelError, kernels
-    q = torch.zeros(1, 3 * 20, device="cuda")
-    with pytest.raises(KernelError, match="head_dim 20"):
-        kernels.paged_attention_generic(q, torch.zeros(1, 20, device="cuda"), torch.zeros(4, 1, 20, device="cuda"),
-                                        torch.zeros(4, 1, 20, device="cuda"),
+    q = torch.zeros(1, 3 * 520, device="cuda")
+    with pytest.raises(KernelError, match="head_dim 520"):
+        kernels.paged_attention_generic(q, torch.zeros(1, 520, device="cuda"), torch.zeros(4, 1, 520, device="cuda"),
+                                        torch.zeros(4, 1, 520, device="cuda"),
                                         torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
                                         torch.zeros(1, dtype=torch.int32, device="cuda"),
-                                        torch.zeros(1, dtype=torch.int32, device="cuda"), 4, 1, 1, 20, 1.0, None)
+                                        torch.zeros(1, dtype=torch.int32, device="cuda"), 4, 1, 1, 520, 1.0, None)
     with pytest.raises(KernelError, match="CUDA tensors only"):
         kernels.silu_mul(torch.zeros(1, 4), torch.zeros(1, 2))
     with pytest.raises(KernelError, match="shapes or strides"):

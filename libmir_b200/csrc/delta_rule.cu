@@ -83,7 +83,14 @@ __global__ void short_conv_tail_kernel(const T* __restrict__ x, long long ldx, f
 //   x          packed projection rows, convolved channel c of token t at x[t * ldx + c]; w [channels, taps]
 //   beta_raw   (t, h) at beta_raw[t * ld_beta + h];  decay_raw (t, j) at decay_raw[t * ld_decay + j], j < decay_width
 //   qkv        out [tokens, channels]; beta out [tokens, heads]; decay out [tokens, decay_width]
-template <typename T, typename TD>
+__device__ __forceinline__ float2 pair_of(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 pair_of(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// PAIRED: every thread works on two neighbouring channels (4- or 8-byte loads of the inputs); needs an even head
+// width, an even number of value channels, an even row stride and a pointer aligned to two elements.
+template <typename T, typename TD, bool PAIRED>
 __global__ void delta_rule_prepare_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w,
                                           const float* __restrict__ tail, const T* __restrict__ beta_raw,
                                           long long ld_beta, const TD* __restrict__ decay_raw, long long ld_decay,
@@ -119,23 +126,59 @@ __global__ void delta_rule_prepare_kernel(const T* __restrict__ x, long long ldx
   // the CTAs of a token (gridDim.y of them, more where a step has few tokens) share its heads and channels out
   const int part = blockIdx.y, parts = gridDim.y;
   const int index = part * blockDim.x + threadIdx.x, stride = parts * blockDim.x;
+  auto convolved_pair = [&](int c) {                           // channels c and c + 1, c even
+    float first = 0.0f, second = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+      const int src = local - (taps - 1) + j;
+      const float2 value = src >= 0 ? pair_of(x + (size_t)(start + src) * ldx + c)
+                                    : pair_of(old + (size_t)(taps - 1 + src) * channels + c);
+      first = fmaf(to_float(w[(size_t)c * taps + j]), value.x, first);
+      second = fmaf(to_float(w[(size_t)(c + 1) * taps + j]), value.y, second);
+    }
+    return make_float2(silu(first), silu(second));
+  };
   for (int unit = part * warps + warp; unit < 2 * kv_heads; unit += parts * warps) {
     float values[kMaxPerLane];
     float square = 0.0f;
+    if (PAIRED) {
 #pragma unroll
-    for (int m = 0; m < kMaxPerLane; ++m) {
-      const int i = lane + 32 * m;
-      values[m] = i < key_dim ? convolved(unit * key_dim + i) : 0.0f;
-      square = fmaf(values[m], values[m], square);
+      for (int m = 0; m < kMaxPerLane; m += 2) {
+        const int i = 2 * lane + 32 * m;
+        const float2 both = i < key_dim ? convolved_pair(unit * key_dim + i) : make_float2(0.0f, 0.0f);
+        values[m] = both.x;
+        values[m + 1] = both.y;
+        square = fmaf(both.x, both.x, fmaf(both.y, both.y, square));
+      }
+    } else {
+#pragma unroll
+      for (int m = 0; m < kMaxPerLane; ++m) {
+        const int i = lane + 32 * m;
+        values[m] = i < key_dim ? convolved(unit * key_dim + i) : 0.0f;
+        square = fmaf(values[m], values[m], square);
+      }
     }
     const float unit_scale = rsqrtf(warp_sum(square) + 1e-6f) * (unit < kv_heads ? q_scale : 1.0f);
+    if (PAIRED) {
 #pragma unroll
-    for (int m = 0; m < kMaxPerLane; ++m) {
-      const int i = lane + 32 * m;
-      if (i < key_dim) out[unit * key_dim + i] = values[m] * unit_scale;
+      for (int m = 0; m < kMaxPerLane; m += 2) {
+        const int i = 2 * lane + 32 * m;
+        if (i < key_dim)
+          *reinterpret_cast<float2*>(out + unit * key_dim + i) = make_float2(values[m] * unit_scale, values[m + 1] * unit_scale);
+      }
+    } else {
+#pragma unroll
+      for (int m = 0; m < kMaxPerLane; ++m) {
+        const int i = lane + 32 * m;
+        if (i < key_dim) out[unit * key_dim + i] = values[m] * unit_scale;
+      }
     }
   }
-  for (int c = 2 * kv_heads * key_dim + index; c < channels; c += stride) out[c] = convolved(c);
+  if (PAIRED) {
+    for (int c = 2 * kv_heads * key_dim + 2 * index; c < channels; c += 2 * stride)
+      *reinterpret_cast<float2*>(out + c) = convolved_pair(c);
+  } else {
+    for (int c = 2 * kv_heads * key_dim + index; c < channels; c += stride) out[c] = convolved(c);
+  }
   for (int h = index; h < heads; h += stride)
     beta[(size_t)token * heads + h] = sigmoid(to_float(beta_raw[(size_t)token * ld_beta + h]));
   const int per_head = decay_width / heads;
@@ -475,15 +518,24 @@ MIR_EXPORT int mir_delta_rule_prepare(int bf16, int decay_f32, const void* x, lo
   int parts = (2 * mir_sm_count() + tokens - 1) / tokens;
   parts = parts < 1 ? 1 : (parts > most ? most : parts);
   int status;
-#define MIR_PREPARE(T, TD)                                                                                             \
-  status = mir_launch("delta_rule_prepare", delta_rule_prepare_kernel<T, TD>, dim3(tokens, parts), dim3(256), 0, stream, 0,   \
-                      (const T*)x, ldx, (const T*)w, (const float*)tail, (const T*)beta_raw, ld_beta,                  \
+  const size_t element = bf16 ? 2 : 4;
+  const bool paired = key_dim % 2 == 0 && (heads * value_dim) % 2 == 0 && ldx % 2 == 0 &&
+                      (uintptr_t)x % (2 * element) == 0 && (uintptr_t)qkv % 8 == 0 && (uintptr_t)tail % 8 == 0;
+#define MIR_PREPARE_AS(T, TD, P)                                                                                       \
+  status = mir_launch("delta_rule_prepare", delta_rule_prepare_kernel<T, TD, P>, dim3(tokens, parts), dim3(256), 0,    \
+                      stream, 0, (const T*)x, ldx, (const T*)w, (const float*)tail, (const T*)beta_raw, ld_beta,       \
                       (const TD*)decay_raw, ld_decay, dt_bias, a_log, row_of_token, query_starts, state_slots,         \
                       positions, qkv, beta, decay, heads, kv_heads, key_dim, value_dim, decay_width, taps)
+#define MIR_PREPARE(T, TD)                                                                                             \
+  do {                                                                                                                 \
+    if (paired) MIR_PREPARE_AS(T, TD, true);                                                                           \
+    else MIR_PREPARE_AS(T, TD, false);                                                                                 \
+  } while (0)
   if (bf16 && decay_f32) MIR_PREPARE(__nv_bfloat16, float);
   else if (bf16) MIR_PREPARE(__nv_bfloat16, __nv_bfloat16);
   else MIR_PREPARE(float, float);
 #undef MIR_PREPARE
+#undef MIR_PREPARE_AS
   if (status != MIR_OK || taps == 1) return status;
   const int threads = channels >= 256 ? 256 : ((channels + 31) / 32) * 32;
   const dim3 tail_grid(rows, (channels + threads - 1) / threads);

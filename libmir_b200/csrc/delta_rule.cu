@@ -385,8 +385,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
 }
 
 // One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * weight * act(gate).
-template <typename T>
-__global__ void gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long ld_gate,
+template <typename T, typename TG>
+__global__ void gated_head_norm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, long long ld_gate,
                                        const float* __restrict__ weight, T* __restrict__ out, int units,
                                        int heads, int value_dim, float eps, int sigmoid_gate) {
   grid_launch_dependents();
@@ -398,7 +398,7 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const T* __r
   float sum = 0.0f;
   for (int d = lane; d < value_dim; d += 32) sum = fmaf(src[d], src[d], sum);
   const float inverse = rsqrtf(warp_sum(sum) / (float)value_dim + eps);
-  const T* gate_row = gate + (size_t)(unit / heads) * ld_gate + (size_t)(unit % heads) * value_dim;
+  const TG* gate_row = gate + (size_t)(unit / heads) * ld_gate + (size_t)(unit % heads) * value_dim;
   for (int d = lane; d < value_dim; d += 32) {
     const float z = to_float(gate_row[d]);
     const float act = sigmoid_gate ? sigmoid(z) : silu(z);
@@ -570,19 +570,22 @@ MIR_EXPORT int mir_delta_rule_scan(int per_channel, const float* qkv, const floa
                             kv_heads, key_dim, value_dim, tokens == rows);
 }
 
-// o [tokens, heads, value_dim] 32-bit; gate element (t, h, d) at gate[t * ld_gate + h * value_dim + d] and out
-// [tokens, heads * value_dim] contiguous, both in the activations' type.
-MIR_EXPORT int mir_gated_head_norm(int bf16, const float* o, const void* gate, long long ld_gate, const float* weight, void* out,
-                                   int tokens, int heads, int value_dim, float eps, int sigmoid_gate,
-                                   cudaStream_t stream) {
+// o [tokens, heads, value_dim] 32-bit; gate element (t, h, d) at gate[t * ld_gate + h * value_dim + d], in the
+// activations' type or (gate_f32) in 32-bit; out [tokens, heads * value_dim] contiguous in the activations' type.
+MIR_EXPORT int mir_gated_head_norm(int bf16, int gate_f32, const float* o, const void* gate, long long ld_gate,
+                                   const float* weight, void* out, int tokens, int heads, int value_dim, float eps,
+                                   int sigmoid_gate, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || value_dim <= 0) { mir_set_error("gated_head_norm: bad sizes"); return MIR_BAD_ARGUMENT; }
   const int units = tokens * heads;
   const dim3 grid((units + 3) / 4), block(32, 4);
+  if (bf16 && gate_f32)
+    return mir_launch("gated_head_norm", gated_head_norm_kernel<__nv_bfloat16, float>, grid, block, 0, stream, 0, o,
+                      (const float*)gate, ld_gate, weight, (__nv_bfloat16*)out, units, heads, value_dim, eps, sigmoid_gate);
   if (bf16)
-    return mir_launch("gated_head_norm", gated_head_norm_kernel<__nv_bfloat16>, grid, block, 0, stream, 0, o,
+    return mir_launch("gated_head_norm", gated_head_norm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, 0, o,
                       (const __nv_bfloat16*)gate, ld_gate, weight, (__nv_bfloat16*)out, units, heads, value_dim, eps,
                       sigmoid_gate);
-  return mir_launch("gated_head_norm", gated_head_norm_kernel<float>, grid, block, 0, stream, 0, o, (const float*)gate,
+  return mir_launch("gated_head_norm", gated_head_norm_kernel<float, float>, grid, block, 0, stream, 0, o, (const float*)gate,
                     ld_gate, weight, (float*)out, units, heads, value_dim, eps, sigmoid_gate);
 }

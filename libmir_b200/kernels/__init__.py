@@ -46,8 +46,8 @@ _SIGNATURES = {
         "mir_delta_rule_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mir_delta_rule_set_lanes": [c_int],
-        "mir_gated_head_norm": [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
-                                c_int, c_void_p],
+        "mir_gated_head_norm": [c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int,
+                                c_float, c_int, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
         "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
@@ -459,15 +459,16 @@ def set_delta_rule_lanes(lanes: int) -> None:
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int,
                     value_dim: int, eps: float, sigmoid_gate: bool) -> None:
     """out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h]) per head, act = sigmoid or silu; o 32-bit
-    [tokens, heads * value_dim], gate a view with unit column stride, out contiguous in gate's dtype."""
+    [tokens, heads * value_dim], gate a view with unit column stride in out's dtype or in float32, out contiguous."""
     _cuda(o, gate, weight, out)
     tokens = o.shape[0]
     _require(o.dtype == torch.float32 and o.is_contiguous() and o.shape[1] == heads * value_dim
              and gate.shape == o.shape and gate.stride(1) == 1 and out.shape == o.shape and out.is_contiguous()
-             and out.dtype == gate.dtype and weight.dtype == torch.float32 and weight.numel() == value_dim,
-             "gated_head_norm: shapes or dtypes do not fit")
+             and gate.dtype in (out.dtype, torch.float32) and weight.dtype == torch.float32
+             and weight.numel() == value_dim, "gated_head_norm: shapes or dtypes do not fit")
     lib = library("core")
-    _check(lib, lib.mir_gated_head_norm(_is_bf16(out), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
+    _check(lib, lib.mir_gated_head_norm(_is_bf16(out), int(gate.dtype == torch.float32), o.data_ptr(), gate.data_ptr(),
+                                        gate.stride(0), weight.data_ptr(),
                                         out.data_ptr(), tokens, heads, value_dim, eps, int(sigmoid_gate), _stream()))
 
 

@@ -62,7 +62,7 @@ class GatedDeltaRule(Mixer):
                 self.segments[name] = (cursor, width)
                 cursor = _pad8(cursor + width)
         self.packed_width = cursor
-        self.w_in = self.w_conv = self.w_a2 = self.w_g2 = self.w_o = None
+        self.w_in = self.w_conv = self.w_a2 = self.w_g2 = self.w_second = self.w_o = None
         self.a_log = self.dt_bias = self.norm = None
 
     def cache_requirement(self):
@@ -112,9 +112,19 @@ class GatedDeltaRule(Mixer):
             self.w_a2 = second_stage(tensors["a2"], s.decay_rank)
         if s.gate == "sigmoid":
             self.w_g2 = second_stage(tensors["g2"], s.gate_rank)
+        self.w_second = None
+        if s.decay == "channel" and s.gate == "sigmoid":
+            # both second stages as one product on the neighbouring segments a1 | g1 of the packed projection: the
+            # weights side by side on the diagonal, zeros elsewhere; the result is 32-bit [decays | gates]
+            ranks = self.w_a2.shape[1] + self.w_g2.shape[1]
+            both = torch.zeros((self.decay_width + self.v_width, ranks), dtype=self.w_a2.dtype, device=self.w_a2.device)
+            both[:self.decay_width, :self.w_a2.shape[1]] = self.w_a2
+            both[self.decay_width:, self.w_a2.shape[1]:] = self.w_g2
+            if self.segments["g1"][0] == self.segments["a1"][0] + self.w_a2.shape[1]:
+                self.w_second, self.w_a2, self.w_g2 = both, None, None
 
     def weight_bytes(self):
-        tensors = (self.w_in, self.w_conv, self.w_a2, self.w_g2, self.w_o, self.a_log, self.dt_bias, self.norm)
+        tensors = (self.w_in, self.w_conv, self.w_a2, self.w_g2, self.w_second, self.w_o, self.a_log, self.dt_bias, self.norm)
         return sum(t.numel() * t.element_size() for t in tensors if t is not None)
 
     def forward(self, ctx, cache, x, residual, overwrite=False):
@@ -125,16 +135,21 @@ class GatedDeltaRule(Mixer):
         packed = ctx.alloc((tokens, self.packed_width), self.env.dtype)
         kernels.linear(x, self.w_in, packed, alloc=ctx.alloc)
         segment = lambda name, width=None: packed[:, self.segments[name][0]:self.segments[name][0] + (width or self.segments[name][1])]
-        if s.decay == "channel":
-            decay = ctx.alloc((tokens, self.decay_width), torch.float32)           # 32-bit: it enters the recurrence
-            kernels.linear(segment("a1", self.w_a2.shape[1]), self.w_a2, decay, alloc=ctx.alloc)
+        if self.w_second is not None:
+            second = ctx.alloc((tokens, self.decay_width + self.v_width), torch.float32)
+            kernels.linear(segment("a1", self.w_second.shape[1]), self.w_second, second, alloc=ctx.alloc)
+            decay, gate = second[:, :self.decay_width], second[:, self.decay_width:]
         else:
-            decay = segment("a")
-        if s.gate == "sigmoid":
-            gate = ctx.alloc((tokens, self.v_width), self.env.dtype)
-            kernels.linear(segment("g1", self.w_g2.shape[1]), self.w_g2, gate, alloc=ctx.alloc)
-        else:
-            gate = segment("g")
+            if s.decay == "channel":
+                decay = ctx.alloc((tokens, self.decay_width), torch.float32)       # 32-bit: it enters the recurrence
+                kernels.linear(segment("a1", self.w_a2.shape[1]), self.w_a2, decay, alloc=ctx.alloc)
+            else:
+                decay = segment("a")
+            if s.gate == "sigmoid":
+                gate = ctx.alloc((tokens, self.v_width), self.env.dtype)
+                kernels.linear(segment("g1", self.w_g2.shape[1]), self.w_g2, gate, alloc=ctx.alloc)
+            else:
+                gate = segment("g")
         # all tokens in parallel: convolutions, unit vectors, sigmoid and the decays; then the recurrence
         prepared = ctx.alloc((tokens, self.conv_channels), torch.float32)
         beta = ctx.alloc((tokens, s.heads), torch.float32)

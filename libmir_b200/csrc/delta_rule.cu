@@ -60,13 +60,13 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ x, long long ldx, c
 template <typename T>
 __global__ void short_conv_tail_kernel(const T* __restrict__ x, long long ldx, float* __restrict__ tail,
                                        const int* __restrict__ query_starts, const int* __restrict__ state_slots,
-                                       const int* __restrict__ positions, int channels, int taps) {
+                                       const int* __restrict__ positions, int channels, int taps, int skip_single) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int row = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const int start = query_starts[row], count = query_starts[row + 1] - start;
-  if (c >= channels || count <= 0 || positions[start] < 0) return;
+  if (c >= channels || count <= 0 || positions[start] < 0 || (skip_single && count == 1)) return;
   float* mine = tail + (size_t)state_slots[row] * (taps - 1) * channels;
   float keep[kMaxTaps];
   for (int j = 0; j < taps - 1; ++j) {
@@ -92,7 +92,7 @@ __device__ __forceinline__ float2 pair_of(const __nv_bfloat16* p) {
 // width, an even number of value channels, an even row stride and a pointer aligned to two elements.
 template <typename T, typename TD, bool PAIRED>
 __global__ void delta_rule_prepare_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w,
-                                          const float* __restrict__ tail, const T* __restrict__ beta_raw,
+                                          float* __restrict__ tail, const T* __restrict__ beta_raw,
                                           long long ld_beta, const TD* __restrict__ decay_raw, long long ld_decay,
                                           const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                           const int* __restrict__ row_of_token, const int* __restrict__ query_starts,
@@ -109,8 +109,11 @@ __global__ void delta_rule_prepare_kernel(const T* __restrict__ x, long long ldx
   const int start = query_starts[row];
   const int local = token - start;
   const int channels = 2 * kv_heads * key_dim + heads * value_dim;
-  const float* old = tail + (size_t)state_slots[row] * (taps - 1) * channels;
+  float* old = tail + (size_t)state_slots[row] * (taps - 1) * channels;
   float* out = qkv + (size_t)token * channels;
+  // A request that brings one token moves its tail on right here: a channel's tail is read by the one thread that
+  // convolves the channel, which then shifts it and appends the token's input (short_conv_tail skips such rows).
+  const bool alone = query_starts[row + 1] - start == 1;
   auto convolved = [&](int c) {
     float acc = 0.0f;
     for (int j = 0; j < taps; ++j) {
@@ -118,6 +121,10 @@ __global__ void delta_rule_prepare_kernel(const T* __restrict__ x, long long ldx
       const float value = src >= 0 ? to_float(x[(size_t)(start + src) * ldx + c])
                                    : old[(size_t)(taps - 1 + src) * channels + c];
       acc = fmaf(to_float(w[(size_t)c * taps + j]), value, acc);
+    }
+    if (alone) {
+      for (int j = 0; j + 2 < taps; ++j) old[(size_t)j * channels + c] = old[(size_t)(j + 1) * channels + c];
+      if (taps > 1) old[(size_t)(taps - 2) * channels + c] = to_float(x[(size_t)token * ldx + c]);
     }
     return silu(acc);
   };
@@ -134,6 +141,11 @@ __global__ void delta_rule_prepare_kernel(const T* __restrict__ x, long long ldx
                                     : pair_of(old + (size_t)(taps - 1 + src) * channels + c);
       first = fmaf(to_float(w[(size_t)c * taps + j]), value.x, first);
       second = fmaf(to_float(w[(size_t)(c + 1) * taps + j]), value.y, second);
+    }
+    if (alone) {
+      for (int j = 0; j + 2 < taps; ++j)
+        *reinterpret_cast<float2*>(old + (size_t)j * channels + c) = pair_of(old + (size_t)(j + 1) * channels + c);
+      if (taps > 1) *reinterpret_cast<float2*>(old + (size_t)(taps - 2) * channels + c) = pair_of(x + (size_t)token * ldx + c);
     }
     return make_float2(silu(first), silu(second));
   };
@@ -489,9 +501,9 @@ MIR_EXPORT int mir_short_conv_silu(int bf16, const void* x, long long ldx, const
   if (status != MIR_OK || taps == 1) return status;
   if (bf16)
     return mir_launch("short_conv_tail", short_conv_tail_kernel<__nv_bfloat16>, tail_grid, dim3(threads), 0, stream, 0,
-                      (const __nv_bfloat16*)x, ldx, tail, query_starts, state_slots, positions, channels, taps);
+                      (const __nv_bfloat16*)x, ldx, tail, query_starts, state_slots, positions, channels, taps, 0);
   return mir_launch("short_conv_tail", short_conv_tail_kernel<float>, tail_grid, dim3(threads), 0, stream, 0,
-                    (const float*)x, ldx, tail, query_starts, state_slots, positions, channels, taps);
+                    (const float*)x, ldx, tail, query_starts, state_slots, positions, channels, taps, 0);
 }
 
 // bf16: the type of x, w and beta_raw (and of decay_raw unless decay_f32).  decay_width: heads, or heads * key_dim for
@@ -523,7 +535,7 @@ MIR_EXPORT int mir_delta_rule_prepare(int bf16, int decay_f32, const void* x, lo
                       (uintptr_t)x % (2 * element) == 0 && (uintptr_t)qkv % 8 == 0 && (uintptr_t)tail % 8 == 0;
 #define MIR_PREPARE_AS(T, TD, P)                                                                                       \
   status = mir_launch("delta_rule_prepare", delta_rule_prepare_kernel<T, TD, P>, dim3(tokens, parts), dim3(256), 0,    \
-                      stream, 0, (const T*)x, ldx, (const T*)w, (const float*)tail, (const T*)beta_raw, ld_beta,       \
+                      stream, 0, (const T*)x, ldx, (const T*)w, tail, (const T*)beta_raw, ld_beta,       \
                       (const TD*)decay_raw, ld_decay, dt_bias, a_log, row_of_token, query_starts, state_slots,         \
                       positions, qkv, beta, decay, heads, kv_heads, key_dim, value_dim, decay_width, taps)
 #define MIR_PREPARE(T, TD)                                                                                             \
@@ -536,14 +548,15 @@ MIR_EXPORT int mir_delta_rule_prepare(int bf16, int decay_f32, const void* x, lo
   else MIR_PREPARE(float, float);
 #undef MIR_PREPARE
 #undef MIR_PREPARE_AS
-  if (status != MIR_OK || taps == 1) return status;
+  // rows of one token have moved their tails on themselves; a step of single tokens needs nothing more
+  if (status != MIR_OK || taps == 1 || tokens == rows) return status;
   const int threads = channels >= 256 ? 256 : ((channels + 31) / 32) * 32;
   const dim3 tail_grid(rows, (channels + threads - 1) / threads);
   if (bf16)
     return mir_launch("short_conv_tail", short_conv_tail_kernel<__nv_bfloat16>, tail_grid, dim3(threads), 0, stream, 0,
-                      (const __nv_bfloat16*)x, ldx, tail, query_starts, state_slots, positions, channels, taps);
+                      (const __nv_bfloat16*)x, ldx, tail, query_starts, state_slots, positions, channels, taps, 1);
   return mir_launch("short_conv_tail", short_conv_tail_kernel<float>, tail_grid, dim3(threads), 0, stream, 0,
-                    (const float*)x, ldx, tail, query_starts, state_slots, positions, channels, taps);
+                    (const float*)x, ldx, tail, query_starts, state_slots, positions, channels, taps, 1);
 }
 
 MIR_EXPORT int mir_delta_rule_set_lanes(int lanes) {

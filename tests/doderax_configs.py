@@ -129,3 +129,40 @@ def make_folder(tmp_path, config: dict, seed: int, dtype: str, sharpen: float = 
         tensors[name] = new.to(kind)
     write_file(folder / "model.safetensors", tensors)
     return folder
+
+
+def random_config(rng) -> dict:
+    """A configuration drawn at random: any layer order, heads and groups, head widths that are no multiples of 8 (or
+    of 4), one to six taps, ranks from 1 on, windows shorter than a page, more kept tokens than the window holds, with
+    and without rotation, window, pair table, logit scale and feed-forward."""
+    def delta(channel):
+        kv_heads = int(rng.integers(1, 4))
+        mixer = _right(kv_heads * int(rng.integers(1, 4)), kv_heads, int(rng.choice([4, 12, 16, 20, 36, 44, 64, 100, 130])),
+                       int(rng.choice([1, 6, 8, 10, 24, 33, 70])), int(rng.integers(1, 7)))
+        if channel:
+            mixer.update(decay_rank=int(rng.integers(1, 21)), gate_rank=int(rng.integers(1, 21)))
+        return mixer
+
+    def attention():
+        kv_heads = int(rng.integers(1, 4))
+        dim = int(rng.choice([8, 12, 16, 20, 24, 40, 64, 128]))
+        vdim = dim if rng.random() < 0.4 else int(rng.choice([4, 6, 8, 12, 24, 40, 96]))
+        rot = (int(rng.choice(list(range(2, dim + 1, 2)))), float(rng.choice([50.0, 10000.0, 250000.0]))) if rng.random() < 0.8 else None
+        mask = (int(rng.integers(1, 60)), int(rng.integers(0, 40))) if rng.random() < 0.85 else None
+        return _left(kv_heads * int(rng.integers(1, 5)), kv_heads, dim, vdim, float(rng.uniform(0.05, 0.4)), rot, mask)
+
+    layers = []
+    for _ in range(int(rng.integers(1, 5))):
+        ff = int(rng.choice([40, 64, 100, 130])) if rng.random() < 0.7 else 0
+        if rng.random() < 0.5:
+            layers.append(_layer("channel_delta", delta(True), ff))
+        else:
+            layers.append(_layer("parallel", {"left": attention(), "right": delta(False)}, ff))
+    config = {"architecture": "Doderax", "vocab": int(rng.integers(30, 300)), "width": int(rng.choice([48, 52, 64, 72, 100, 136, 50])),
+              "norm": {"eps": float(rng.choice([1e-5, 1e-6, 1e-4]))}, "layers": layers}
+    if rng.random() < 0.7:
+        config["logit_scale"] = float(rng.uniform(0.2, 3.0))
+    if rng.random() < 0.7:
+        config["embedding"] = {"bigram": {"buckets": int(rng.integers(2, 200)), "mul_prev": int(rng.integers(1, 1000)),
+                                          "mul_cur": int(rng.integers(1, 1000))}}
+    return config

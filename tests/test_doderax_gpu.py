@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_doderax as plain
-from doderax_configs import ALL, PAGE_SIZES, make_folder
+from doderax_configs import ALL, PAGE_SIZES, make_folder, random_config
 from helpers import TOL, Trace, random_ids, run_trace
 
 pytestmark = pytest.mark.gpu
@@ -561,3 +561,30 @@ def test_generate_command_line(tmp_path):
     sampled = [subprocess.run(command + ["--prompt-ids", "1,2,3", "--temperature", "0.9", "--top-k", "20", "--seed", "4"],
                               capture_output=True, text=True, timeout=600).stdout for _ in range(2)]
     assert sampled[0] == sampled[1] and "finish_reason=" in sampled[0]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Sizes nobody chose: a prompt whole, token by token, in portions and as a prompt followed by decoding, in both
+    dtypes, against the plain implementation (32-bit: every position within 2e-4 of its logits' root mean square and
+    the same bits under every cut; bfloat16: nine positions in ten within the tolerance)."""
+    rng = np.random.default_rng(500 + seed)
+    config = random_config(rng)
+    page = int(rng.choice([4, 8, 16]))
+    ids = random_ids(rng, config["vocab"], 100)
+    for dtype in ("float32", "bfloat16"):
+        folder = make_folder(tmp_path / dtype, config, seed=seed, dtype=dtype)
+        want = reference(folder, ids)
+        model = load(folder, dtype, page, 80)
+        outputs = [feed(model, "whole", ids, [len(ids)]), feed(model, "single", ids, [1]),
+                   feed(model, "portions", ids, [2, 5, 1, 33, 3, 16, 2, 7]), feed(model, "late", ids, [80, 1])]
+        for got in outputs:
+            relative = np.sqrt(((got - want) ** 2).mean(-1)) / np.sqrt((want ** 2).mean(-1))
+            assert np.isfinite(relative).all(), json.dumps(config)
+            if dtype == "float32":
+                assert relative.max() <= 2e-4, f"{relative.max():.3e} at {int(relative.argmax())}: {json.dumps(config)}"
+            else:
+                assert np.quantile(relative, 0.9) <= TOL[dtype], f"{np.quantile(relative, 0.9):.3e}: {json.dumps(config)}"
+        if dtype == "float32":
+            assert all(np.array_equal(outputs[0], other) for other in outputs[1:]), json.dumps(config)
+        model.unload()

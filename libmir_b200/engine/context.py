@@ -149,7 +149,8 @@ class StepContext(PartContext):
         norm_weight = norm.weight if (norm is not None and norm.foldable) else None
         if (not kernels.FUSE_NORM_INTO_PRODUCT or norm_weight is None or self.dtype != torch.bfloat16
                 or residual.shape[0] > kernels.few_rows_max()
-                or norm_weight.numel() != residual.shape[1]):
+                or norm_weight.numel() != residual.shape[1]
+                or residual.shape[1] % 16 != 0):           # (whole 16-column tiles of sums; rows that TMA can read)
             kernels.linear(x, weight, residual, bias, accumulate=True)
             self.residual_stats = None
             return

@@ -842,27 +842,33 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
     return bool(wrote.value)
 
 
-def linear_gelu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, alloc=None) -> None:
+def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None) -> None:
     """out = gelu_tanh(x . weight^T) in the activations' dtype.  bfloat16: one kernel with the activation in its
-    epilogue where our tcgen05 products take the rows (up to few_rows_max on the weight-streaming kernel, from
-    tensor_core_min_rows on the many-rows kernel; the approximate hardware tanh, whose error is below bfloat16's
-    rounding), else the library product and the activation kernel.  float32: the 32-bit product and that kernel."""
-    _cuda(x, weight, out)
-    m, k = x.shape
+    epilogue where our tcgen05 products take the rows (up to few_rows_max on the weight-streaming kernel, where x may
+    be a NormedResidual, a norm folded into this product; from tensor_core_min_rows on the many-rows kernel; the
+    approximate hardware tanh, whose error is below bfloat16's rounding), else the library product and the activation
+    kernel.  float32: the 32-bit product and that kernel."""
+    lazy = x if isinstance(x, NormedResidual) else None
+    rows = lazy.weighted if lazy is not None else x
+    _cuda(rows, weight, out)
+    m, k = rows.shape
     n = weight.shape[0]
-    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k % 8 == 0
-            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.stride(1) == 1 and out.stride(1) == 1
+    if (rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k % 8 == 0
+            and rows.stride(0) % 8 == 0 and rows.data_ptr() % 16 == 0 and rows.stride(1) == 1 and out.stride(1) == 1
             and weight.is_contiguous() and out.shape == (m, n) and FUSE_GELU_INTO_PRODUCT):
         lib = library("bf16")
-        if 0 < m <= min(get_option("few_rows_max"), STREAM_MAX_ROWS):
-            _check(lib, lib.mir_gemm_tc_stream_bf16(MODE_GELU, x.data_ptr(), x.stride(0), weight.data_ptr(), None,
-                                                    out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, 0.0, None, None,
-                                                    None, 0, _stream()))
+        if 0 < m <= min(get_option("few_rows_max"), STREAM_MAX_ROWS) and (lazy is None or m <= NORM_STAT_STRIDE):
+            _check(lib, lib.mir_gemm_tc_stream_bf16(
+                MODE_GELU, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None, out.data_ptr(), out.stride(0), m, n,
+                k, 0, lazy.sumsq.data_ptr() if lazy is not None else None, lazy.tiles if lazy is not None else 0,
+                lazy.eps if lazy is not None else 0.0, None, None, None, 0, _stream()))
             return
-        if m >= get_option("tensor_core_min_rows"):
-            _check(lib, lib.mir_gemm_tc_bf16(MODE_GELU, x.data_ptr(), x.stride(0), weight.data_ptr(), None,
+        if lazy is None and m >= get_option("tensor_core_min_rows"):
+            _check(lib, lib.mir_gemm_tc_bf16(MODE_GELU, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None,
                                              out.data_ptr(), out.stride(0), m, n, k, 0, _stream()))
             return
+    if lazy is not None:
+        x = lazy.materialize(alloc)
     linear(x, weight, out, alloc=alloc)
     _require(out.is_contiguous(), "linear_gelu: a contiguous result is needed")
     gelu_tanh(out)

@@ -127,15 +127,26 @@ class ParallelBlock(Block):
         return self.mixer_norm
 
     def forward(self, ctx, cache, residual):
-        # the residual changes twice before the next norm sees it, and the normed rows are read twice: the norm runs
-        # as a kernel, and no product prepares the next one
-        x = (self.mixer_norm.forward(ctx, residual) if self.mixer_norm is not None else ctx.cast_residual(residual))
+        # Both branches read the same normed rows.  If the product that last added into the residual left what this
+        # norm needs (sums of squares and weighted rows: a few-rows step), and both branches can take the norm over
+        # into their first products, no norm kernel runs; else the norm runs once as a kernel.
+        after = ctx.norm_after_block
+        consumers = [part for part in (self.mixer, self.feed_forward) if part is not None]
+        foldable = self.mixer_norm is not None and self.mixer_norm.foldable and \
+            all(part.takes_normed_residual for part in consumers)
+        if self.mixer_norm is None:
+            x = ctx.cast_residual(residual)
+        else:
+            x = self.mixer_norm.forward(ctx, residual, lazy=True) if foldable else self.mixer_norm.forward(ctx, residual)
+        # the branch that adds into the residual last may prepare the norm the next block starts with
         ctx.residual_stats = None
-        ctx.upcoming_norm = None
+        ctx.upcoming_norm = after if self.feed_forward is None else None
         self.mixer.forward(ctx, cache, x, residual)
         if self.feed_forward is not None:
+            ctx.residual_stats = None
+            ctx.upcoming_norm = after
             self.feed_forward.forward(ctx, x, residual)
-        ctx.residual_stats = None
+        ctx.upcoming_norm = None
 
 
 ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock}

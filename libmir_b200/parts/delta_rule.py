@@ -34,6 +34,7 @@ def _pad8(n: int) -> int:
 
 class GatedDeltaRule(Mixer):
     graph_safe = True          # the batch is read from device tensors only; padding rows (position < 0) are skipped
+    takes_normed_residual = True   # x is used by one product only, which can take a folded norm over
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -51,6 +51,7 @@ class GeluMlp(FeedForward):
     epilogue of the up projection where our own products run it, else on the product's rows, in place."""
 
     graph_safe = True
+    takes_normed_residual = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -69,6 +70,6 @@ class GeluMlp(FeedForward):
         return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, ctx, x, residual):
-        hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)
+        hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)   # (x may be a folded norm)
         kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc)     # the activation in the product's epilogue
         ctx.accumulate(hidden, self.w_down, residual)

@@ -36,6 +36,10 @@ class SideBySide(Mixer):
         return all(branch.graph_safe for branch in self.branches)
 
     @property
+    def takes_normed_residual(self):
+        return all(branch.takes_normed_residual for branch in self.branches)
+
+    @property
     def portion_multiple(self):
         import math
         return math.lcm(*[max(1, int(branch.portion_multiple)) for branch in self.branches])

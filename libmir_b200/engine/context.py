@@ -150,7 +150,7 @@ class StepContext(PartContext):
         if (not kernels.FUSE_NORM_INTO_PRODUCT or norm_weight is None or self.dtype != torch.bfloat16
                 or residual.shape[0] > kernels.few_rows_max()
                 or norm_weight.numel() != residual.shape[1]
-                or residual.shape[1] % 16 != 0):           # (whole 16-column tiles of sums; rows that TMA can read)
+                or residual.shape[1] % 8 != 0):            # (the weighted rows are read by TMA: 16-byte row strides)
             kernels.linear(x, weight, residual, bias, accumulate=True)
             self.residual_stats = None
             return

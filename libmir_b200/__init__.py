@@ -1,4 +1,6 @@
-"""libmir_b200: a single-GPU inference engine for the dense SwiGLU decoder on NVIDIA B200 (sm_100a).
+"""libmir_b200: a single-GPU inference engine on NVIDIA B200 (sm_100a) for the dense SwiGLU decoder (Llama / Qwen)
+and for Doderax (recurrent gated-delta-rule layers, some beside windowed attention): one registry, loader, cache
+manager, step function, scheduler and sampler for both.
 
     from libmir_b200 import Library, RuntimeConfig, GenerationRequest, GenerationOverrides
     model = Library(RuntimeConfig()).load("/path/to/model")

@@ -39,7 +39,7 @@ def main(argv=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens that live requests hold at any time")
     parser.add_argument("--page-size", type=int, default=16)
-    parser.add_argument("--max-requests", type=int, default=8)
+    parser.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests live at any time")
     parser.add_argument("--decode-graphs", action="store_true",
                         help="run steps of single tokens as replays of captured CUDA graphs, as generation does")
     parser.add_argument("--report", help="write launch counts, kernel error flags and cache counters to this file")

@@ -62,7 +62,7 @@ class PagedKv:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
-    value_head_dim: Optional[int] = None
+    value_head_dim: Optional[int] = None     # 0: one vector per token and kv head only (a latent read as key and as value)
     keep_first: int = 0           # with a window: the request's first tokens whose pages are never given back
 
     @property
@@ -148,13 +148,27 @@ class RmsNormSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """Frequencies stretched by `factor` where a pair turns fewer than `slow` times over `original` positions, kept
+    where it turns more than `fast` times, blended linearly (by pair index) in between; cos and sin are multiplied by
+    0.1 ln(factor) + 1."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class RotarySpec(PartSpec):
-    """Half-split rotary position encoding of the first `rotary_dim` dims of a head."""
+    """Rotary position encoding of the first `rotary_dim` dims of a head.  `layout` "half": dims i and i + r/2 form a
+    pair; "interleaved": dims 2i and 2i + 1.  `scaling`: config.RopeScaling (the llama3 rule), YarnScaling or None."""
 
     head_dim: int = 0
     rotary_dim: int = 0
     theta: float = 10000.0
-    scaling: Any = None           # config.RopeScaling or None
+    scaling: Any = None
+    layout: str = "half"
     kind: str = field(init=False, default="rotary")
 
 
@@ -190,11 +204,70 @@ class SwiGluSpec(PartSpec):
 
 @dataclass(frozen=True)
 class GeluMlpSpec(PartSpec):
-    """down(gelu_tanh(up(x))): a dense feed-forward without a gate."""
+    """down(gelu(up(x))): a dense feed-forward without a gate.  `activation`: "gelu_tanh" (the tanh form) or
+    "gelu_erf" (the exact form)."""
 
     hidden_size: int = 0
     intermediate_size: int = 0
+    activation: str = "gelu_tanh"
     kind: str = field(init=False, default="gelu_mlp")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Softmax attention whose keys and values are up-projections of one cached latent per token, beside one rotated
+    key part shared by all heads (parts/latent_attention.py).  Per head `head_dim` unrotated and `rotary_dim` rotated
+    query / key dims and `value_dim` value dims; `q_rank` and `kv_rank` are the widths of the two latents.
+    `gate`: the concatenated heads are multiplied by the sigmoid of a projection of the mixer's input."""
+
+    hidden_size: int = 0
+    heads: int = 0
+    head_dim: int = 0
+    rotary_dim: int = 0
+    value_dim: int = 0
+    q_rank: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    norm_eps: float = 1e-5
+    gate: bool = True
+    position: Optional[PartSpec] = None
+    kind: str = field(init=False, default="latent_attention")
+
+
+@dataclass(frozen=True)
+class WkvSpec(PartSpec):
+    """Time mixing with a matrix state per head, a decay per head and key channel from a low-rank pair with tanh
+    between (rank `decay_rank`), a bonus for the current token, and inputs blended with the token before
+    (parts/wkv.py)."""
+
+    hidden_size: int = 0
+    heads: int = 0
+    head_dim: int = 0
+    decay_rank: int = 0
+    norm_eps: float = 1e-5
+    kind: str = field(init=False, default="wkv")
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec(PartSpec):
+    """A mixture of gated experts (down(silu(gate x) * up x)), `top` of `experts` per token (parts/experts.py).
+    Router: 32-bit logits, `score` "sigmoid"; with `correction` a stored bias is added to the scores for the choice
+    only; experts lie in `groups` equal groups of neighbours of which the `keep_groups` best (by the sum of a group's
+    two largest choice scores) may be chosen from; the chosen scores are divided by their sum and multiplied by
+    `scale`.  `shared_size` > 0: an expert of that width runs for every token, times the sigmoid of one number per
+    token if `shared_gate`."""
+
+    hidden_size: int = 0
+    expert_size: int = 0
+    experts: int = 0
+    top: int = 0
+    groups: int = 1
+    keep_groups: int = 1
+    scale: float = 1.0
+    correction: bool = True
+    shared_size: int = 0
+    shared_gate: bool = True
+    kind: str = field(init=False, default="routed_experts")
 
 
 @dataclass(frozen=True)
@@ -248,8 +321,9 @@ class LayerSpec:
 
     `prefix` is the checkpoint prefix of the layer; `names` maps each slot of the
     arrangement to the sub-prefix of its tensors, so names are data of the architecture.
-    Arrangements: "pre_norm" (a norm before each of the two branches, one after the other) and "parallel" (one
-    norm, `mixer_norm`, whose output both branches read; `feed_forward_norm` is None).
+    Arrangements: "pre_norm" (a norm before each of the two branches, one after the other) and "parallel" (both
+    branches read the same residual and their results are added to it together: through one norm, `mixer_norm`, if
+    `feed_forward_norm` is None, else each through a norm of its own).
     """
 
     prefix: str
@@ -271,6 +345,18 @@ class ScheduleEntry:
 
     layer: int
     cache_of: Optional[int] = None
+    opens_pass: Optional[int] = None      # the number of the pass of ModelSpec.loop that starts with this entry
+
+
+@dataclass(frozen=True)
+class LoopSpec:
+    """A run of layers that is repeated with the same weights (every repeat is a schedule entry of its own, so it has
+    a cache or state of its own).  Before each pass the row `pass` of the tensor `step_tensor` [passes, hidden] is
+    added to the residual, and before each pass but the first, ahead of that, the embedding's output."""
+
+    passes: int
+    step_tensor: Optional[str] = None
+    add_embedding: bool = True
 
 
 @dataclass(frozen=True)
@@ -292,6 +378,7 @@ class HeadSpec:
     hidden_size: int
     tied: bool = False
     scale: float = 1.0
+    softcap: Optional[float] = None       # logits <- softcap * tanh(logits / softcap)
 
 
 @dataclass(frozen=True)
@@ -307,6 +394,7 @@ class ModelSpec:
     final_norm_name: str
     head: HeadSpec
     strip_prefixes: tuple = ()      # checkpoint prefixes that may wrap every name
+    loop: Optional[LoopSpec] = None
 
     def validate(self) -> None:
         if not self.layers:
@@ -321,3 +409,5 @@ class ModelSpec:
                 if self.schedule[entry.cache_of].cache_of is not None:
                     raise ConfigError(f"schedule entry {index} reads the cache of entry {entry.cache_of}, "
                                       "which has no cache of its own")
+            if entry.opens_pass is not None and (self.loop is None or not 0 <= entry.opens_pass < self.loop.passes):
+                raise ConfigError(f"schedule entry {index} opens pass {entry.opens_pass} of a loop the model does not have")

@@ -1,5 +1,5 @@
 // Paged grouped-query softmax attention, one code path for portions of prompts and for decoded
-// tokens, any head size up to 512 (16-byte loads where it is a multiple of 8), any number of heads and groups,
+// tokens, any head size up to 640 (16-byte loads where it is a multiple of 8), any number of heads and groups,
 // optional sliding window, float or bf16 storage.  One warp per (token, query head).
 //
 // This is the reference kernel of the engine: the 32-bit path always runs it, and the bf16 path
@@ -13,13 +13,15 @@
 // denominator, all in 32-bit; key j is visible to the query at position p iff j <= p and
 // (window == 0 or j > p - window or j < keep_first): with a window, the first keep_first keys of a request stay
 // visible to every later query (they keep their pages and their true positions).  Values may be narrower or wider
-// than keys (value_dim).  A query walks over the kept keys first, then over its window.
+// than keys (value_dim).  A query walks over the kept keys first, then over its window.  Consecutive value rows
+// lie value_row_width elements apart: value_dim in a cache of their own, head_dim where the values are the first
+// value_dim elements of the keys themselves (a latent that is read both ways; v_pages is then k_pages).
 #include <cfloat>
 #include "common.cuh"
 
 using namespace mir;
 
-constexpr int kMaxHeadDim = 512;
+constexpr int kMaxHeadDim = 640;
 constexpr int kWarpsPerBlock = 4;
 
 template <typename T>
@@ -27,7 +29,7 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, size_t q_token_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ row_of_token, const int* __restrict__ positions, int page_size, int heads, int kv_heads,
-    int head_dim, int value_dim, float scale, int window, int keep_first) {
+    int head_dim, int value_dim, int value_row_width, float scale, int window, int keep_first) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int lane = threadIdx.x;
   const int warp = threadIdx.y;
@@ -89,7 +91,7 @@ __global__ void paged_attention_generic_kernel(
     for (int j = 0; j < keys_here; ++j) {
       const float w = __shfl_sync(0xffffffffu, weight, j);
       const size_t offset = __shfl_sync(0xffffffffu, key_offset, j);
-      const T* v_row = v_pages + offset * value_dim;
+      const T* v_row = v_pages + offset * value_row_width;
 #pragma unroll
       for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int d = lane + 32 * i;
@@ -113,7 +115,8 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
                                            const void* k_pages, const void* v_pages, const int* block_table,
                                            int table_width, const int* row_of_token, const int* positions, int tokens,
                                            int page_size, int heads, int kv_heads, int head_dim, int value_dim,
-                                           float scale, int window, int keep_first, cudaStream_t stream) {
+                                           float scale, int window, int keep_first, int value_row_width,
+                                           cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 ||
       window < 0 || keep_first < 0) {
@@ -129,17 +132,18 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
     mir_set_error("paged_attention: value_dim %d is not in [1, %d]", value_dim, kMaxHeadDim);
     return MIR_BAD_ARGUMENT;
   }
+  if (value_row_width <= 0) value_row_width = value_dim;
   const dim3 grid(tokens, (heads + kWarpsPerBlock - 1) / kWarpsPerBlock);
   const dim3 block(32, kWarpsPerBlock);
   if (bf16)
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const __nv_bfloat16*)q, (size_t)q_token_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pages,
         (const __nv_bfloat16*)v_pages, block_table, table_width, row_of_token, positions, page_size, heads, kv_heads,
-        head_dim, value_dim, scale, window, keep_first);
+        head_dim, value_dim, value_row_width, scale, window, keep_first);
   else
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const float*)q, (size_t)q_token_stride, (float*)out, (const float*)k_pages, (const float*)v_pages,
-        block_table, table_width, row_of_token, positions, page_size, heads, kv_heads, head_dim, value_dim, scale,
-        window, keep_first);
+        block_table, table_width, row_of_token, positions, page_size, heads, kv_heads, head_dim, value_dim,
+        value_row_width, scale, window, keep_first);
   return mir_check_launch("paged_attention_generic");
 }

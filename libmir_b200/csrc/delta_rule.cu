@@ -396,11 +396,12 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
   }
 }
 
-// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * weight * act(gate).
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * weight * act(gate); the weight is [value_dim], the
+// same for every head, or (weight_per_head) [heads, value_dim].
 template <typename T, typename TG>
 __global__ void gated_head_norm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, long long ld_gate,
                                        const float* __restrict__ weight, T* __restrict__ out, int units,
-                                       int heads, int value_dim, float eps, int sigmoid_gate) {
+                                       int heads, int value_dim, float eps, int sigmoid_gate, int weight_per_head) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int unit = blockIdx.x * blockDim.y + threadIdx.y;       // token * heads + head
@@ -411,10 +412,11 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const TG* __
   for (int d = lane; d < value_dim; d += 32) sum = fmaf(src[d], src[d], sum);
   const float inverse = rsqrtf(warp_sum(sum) / (float)value_dim + eps);
   const TG* gate_row = gate + (size_t)(unit / heads) * ld_gate + (size_t)(unit % heads) * value_dim;
+  const float* scale = weight + (weight_per_head ? (size_t)(unit % heads) * value_dim : 0);
   for (int d = lane; d < value_dim; d += 32) {
     const float z = to_float(gate_row[d]);
     const float act = sigmoid_gate ? sigmoid(z) : silu(z);
-    out[(size_t)unit * value_dim + d] = from_float<T>(src[d] * inverse * weight[d] * act);
+    out[(size_t)unit * value_dim + d] = from_float<T>(src[d] * inverse * scale[d] * act);
   }
 }
 
@@ -587,18 +589,19 @@ MIR_EXPORT int mir_delta_rule_scan(int per_channel, const float* qkv, const floa
 // activations' type or (gate_f32) in 32-bit; out [tokens, heads * value_dim] contiguous in the activations' type.
 MIR_EXPORT int mir_gated_head_norm(int bf16, int gate_f32, const float* o, const void* gate, long long ld_gate,
                                    const float* weight, void* out, int tokens, int heads, int value_dim, float eps,
-                                   int sigmoid_gate, cudaStream_t stream) {
+                                   int sigmoid_gate, int weight_per_head, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || value_dim <= 0) { mir_set_error("gated_head_norm: bad sizes"); return MIR_BAD_ARGUMENT; }
   const int units = tokens * heads;
   const dim3 grid((units + 3) / 4), block(32, 4);
   if (bf16 && gate_f32)
     return mir_launch("gated_head_norm", gated_head_norm_kernel<__nv_bfloat16, float>, grid, block, 0, stream, 0, o,
-                      (const float*)gate, ld_gate, weight, (__nv_bfloat16*)out, units, heads, value_dim, eps, sigmoid_gate);
+                      (const float*)gate, ld_gate, weight, (__nv_bfloat16*)out, units, heads, value_dim, eps, sigmoid_gate,
+                      weight_per_head);
   if (bf16)
     return mir_launch("gated_head_norm", gated_head_norm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, 0, o,
                       (const __nv_bfloat16*)gate, ld_gate, weight, (__nv_bfloat16*)out, units, heads, value_dim, eps,
-                      sigmoid_gate);
+                      sigmoid_gate, weight_per_head);
   return mir_launch("gated_head_norm", gated_head_norm_kernel<float, float>, grid, block, 0, stream, 0, o, (const float*)gate,
-                    ld_gate, weight, (float*)out, units, heads, value_dim, eps, sigmoid_gate);
+                    ld_gate, weight, (float*)out, units, heads, value_dim, eps, sigmoid_gate, weight_per_head);
 }

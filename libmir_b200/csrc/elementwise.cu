@@ -273,6 +273,56 @@ MIR_EXPORT int mir_embed_pairs(int bf16, const void* table, const void* pairs, c
                     (const float*)pairs, ids, previous, out, hidden, vocab, buckets, mul_previous, mul_current, scale);
 }
 
+// x <- act(x) in place: kind 1 the exact GELU 0.5 x (1 + erf(x / sqrt 2)), kind 2 tanh; computed in 32-bit.
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ x, size_t total, int kind) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const float z = to_float(x[index]);
+  x[index] = from_float<T>(kind == 1 ? 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)) : tanhf(z));
+}
+
+// x <- cap * tanh(x / cap) on 32-bit logits.
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index < total) x[index] = cap * tanhf(x[index] / cap);
+}
+
+// residual[r, :] += rows[r, :] (if given) + vector (if given): what a pass of a looped run of layers starts with.
+__global__ void add_rows_kernel(float* __restrict__ residual, const float* __restrict__ rows,
+                                const float* __restrict__ vector, int hidden, size_t total) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  float v = residual[index];
+  if (rows != nullptr) v += rows[index];
+  if (vector != nullptr) v += vector[index % hidden];
+  residual[index] = v;
+}
+
+// Two norms of the same rows: out_a = x * s * weight_a, out_b = x * s * weight_b with one s = rsqrt(mean(x^2) + eps).
+template <typename Tout>
+__global__ void rms_norm_pair_kernel(const float* __restrict__ x, const float* __restrict__ weight_a,
+                                     const float* __restrict__ weight_b, Tout* __restrict__ out_a,
+                                     Tout* __restrict__ out_b, int hidden, float eps) {
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  const float* src = x + (size_t)row * hidden;
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = src[c];
+    sum = fmaf(v, v, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float inverse = rsqrtf(sum / (float)hidden + eps);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = src[c] * inverse;
+    out_a[(size_t)row * hidden + c] = from_float<Tout>(v * weight_a[c]);
+    out_b[(size_t)row * hidden + c] = from_float<Tout>(v * weight_b[c]);
+  }
+}
+
 MIR_EXPORT int mir_gelu_tanh(int bf16, void* x, size_t total, cudaStream_t stream) {
   if (bf16 && total % 8 == 0 && ((uintptr_t)x & 15) == 0) LAUNCH_1D(gelu_tanh_bf16x8_kernel, total / 8, (__nv_bfloat16*)x, total / 8);
   else if (bf16) LAUNCH_1D(gelu_tanh_kernel, total, (__nv_bfloat16*)x, total);
@@ -318,6 +368,39 @@ MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void*
                       (__nv_bfloat16*)out, rows, hidden, eps);
   return mir_launch("rms_norm", rms_norm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, 0, x, weight,
                     (float*)out, rows, hidden, eps);
+}
+
+MIR_EXPORT int mir_activation(int kind, int bf16, void* x, size_t total, cudaStream_t stream) {
+  if (kind != 1 && kind != 2) { mir_set_error("activation: unknown kind %d", kind); return MIR_BAD_ARGUMENT; }
+  if (bf16) LAUNCH_1D(activation_kernel, total, (__nv_bfloat16*)x, total, kind);
+  else LAUNCH_1D(activation_kernel, total, (float*)x, total, kind);
+  return mir_check_launch(kind == 1 ? "gelu_erf" : "tanh");
+}
+
+MIR_EXPORT int mir_softcap(float* x, size_t total, float cap, cudaStream_t stream) {
+  if (!(cap > 0.0f)) { mir_set_error("softcap: the cap must be greater than zero"); return MIR_BAD_ARGUMENT; }
+  LAUNCH_1D(softcap_kernel, total, x, total, cap);
+  return mir_check_launch("softcap");
+}
+
+MIR_EXPORT int mir_add_rows(float* residual, const float* rows, const float* vector, int n_rows, int hidden,
+                            cudaStream_t stream) {
+  if (n_rows < 0 || hidden <= 0) { mir_set_error("add_rows: bad sizes"); return MIR_BAD_ARGUMENT; }
+  const size_t total = (size_t)n_rows * hidden;
+  LAUNCH_1D(add_rows_kernel, total, residual, rows, vector, hidden, total);
+  return mir_check_launch("add_rows");
+}
+
+MIR_EXPORT int mir_rms_norm_pair(int bf16, const float* x, const float* weight_a, const float* weight_b, void* out_a,
+                                 void* out_b, int n_rows, int hidden, float eps, cudaStream_t stream) {
+  if (n_rows == 0) return MIR_OK;
+  if (n_rows < 0 || hidden <= 0) { mir_set_error("rms_norm_pair: bad sizes"); return MIR_BAD_ARGUMENT; }
+  const int threads = hidden >= 2048 ? 512 : 256;
+  if (bf16)
+    return mir_launch("rms_norm_pair", rms_norm_pair_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 0, x,
+                      weight_a, weight_b, (__nv_bfloat16*)out_a, (__nv_bfloat16*)out_b, hidden, eps);
+  return mir_launch("rms_norm_pair", rms_norm_pair_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, 0, x, weight_a,
+                    weight_b, (float*)out_a, (float*)out_b, hidden, eps);
 }
 
 MIR_EXPORT int mir_silu_mul(int bf16, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {

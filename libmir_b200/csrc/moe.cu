@@ -1,0 +1,342 @@
+// Kernels of a mixture of gated experts.  P = tokens * top pairs of (token, chosen expert); pair p = token * top + slot.
+//
+//   moe_route     per token: 32-bit router logits, sigmoid scores, choice among the experts of the best groups by
+//                 score + correction, weights = chosen scores / their sum * scale; and the shared expert's gate
+//   moe_sort      the pairs ordered by expert (a stable counting sort inside one CTA), each expert's range, and the
+//                 list of tiles of kExpertTile pairs of one expert that the grouped products walk over
+//   moe_grouped   products on the sorted pairs with each pair's own expert's weights: hidden = silu(Wg x) * (Wu x)
+//                 from the tokens' rows, and the down projection of the hidden rows into one 32-bit row per pair
+//   moe_combine   residual[t] += sum over slots of weight * the pair's row (+ gate * the shared expert's row)
+// Everything the host needs to launch them is known before the step: no count is read back.
+#include <cfloat>
+#include "common.cuh"
+
+using namespace mir;
+
+namespace {
+
+constexpr int kExpertTile = 8;        // pairs of one expert that a CTA of the grouped product takes
+constexpr int kMaxExperts = 1024;
+
+__device__ __forceinline__ float sigmoid_of(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// One CTA per token.  Shared memory: score[E] | choice[E] | group score[groups].
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
+                                 const float* __restrict__ correction, const float* __restrict__ shared_gate_w,
+                                 int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ shared_gate,
+                                 int width, int experts, int top, int groups, int keep, float scale) {
+  extern __shared__ float route_shared[];
+  float* score = route_shared;
+  float* choice = route_shared + experts;
+  float* group_score = route_shared + 2 * experts;
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int token = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const T* x = h + (size_t)token * ld;
+  for (int e = warp; e < experts + (shared_gate_w != nullptr ? 1 : 0); e += warps) {
+    const float* w = e < experts ? router + (size_t)e * width : shared_gate_w;
+    float sum = 0.0f;
+    for (int c = lane; c < width; c += 32) sum = fmaf(to_float(x[c]), w[c], sum);
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      const float s = sigmoid_of(sum);
+      if (e < experts) {
+        score[e] = s;
+        choice[e] = correction != nullptr ? s + correction[e] : s;
+      } else {
+        shared_gate[token] = s;
+      }
+    }
+  }
+  __syncthreads();
+  const int per_group = experts / groups;
+  // a group's score: the sum of its two largest choice scores (of its one score where a group is one expert)
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float first = -FLT_MAX, second = -FLT_MAX;
+    for (int e = g * per_group; e < (g + 1) * per_group; ++e) {
+      const float c = choice[e];
+      if (c > first) { second = first; first = c; }
+      else if (c > second) second = c;
+    }
+    group_score[g] = per_group > 1 ? first + second : first;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  // experts of all but the `keep` best groups cannot be chosen: their choice scores count as minus infinity
+  if (keep < groups) {
+    for (int round = 0; round < groups - keep; ++round) {
+      int worst = -1;
+      float low = FLT_MAX;
+      for (int g = groups - 1; g >= 0; --g)                      // among equals the later group goes first
+        if (group_score[g] != FLT_MAX && group_score[g] < low) { low = group_score[g]; worst = g; }
+      if (worst < 0) break;
+      group_score[worst] = FLT_MAX;                              // marked as dropped
+      for (int e = worst * per_group; e < (worst + 1) * per_group; ++e) choice[e] = -FLT_MAX;
+    }
+  }
+  float total = 0.0f;
+  for (int slot = 0; slot < top; ++slot) {
+    int best = -1;
+    float high = -FLT_MAX;
+    for (int e = 0; e < experts; ++e)
+      if (choice[e] > high) { high = choice[e]; best = e; }
+    if (best < 0) best = 0;                                      // (fewer choosable experts than top: not a valid model)
+    choice[best] = -FLT_MAX;
+    ids[(size_t)token * top + slot] = best;
+    weights[(size_t)token * top + slot] = score[best];
+    total += score[best];
+  }
+  const float factor = scale / (total + 1e-20f);
+  for (int slot = 0; slot < top; ++slot) weights[(size_t)token * top + slot] *= factor;
+}
+
+// One CTA of 1024 threads.  order[i] = the i-th pair when the pairs are sorted by expert (pairs of one expert stay in
+// their own order); offsets[e] .. offsets[e + 1] is expert e's range in it; tiles[2 n], tiles[2 n + 1] = expert and
+// first sorted pair of the n-th tile, tile_count[0] = how many there are.
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ order,
+                                int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ tile_count) {
+  __shared__ int count[kMaxExperts + 1];
+  __shared__ int first[kMaxExperts + 1];
+  __shared__ int first_tile[kMaxExperts + 1];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int e = warp; e < experts; e += warps) {
+    int n = 0;
+    for (int p = lane; p - lane < pairs; p += 32) n += __popc(__ballot_sync(0xffffffffu, p < pairs && ids[p] == e));
+    if (lane == 0) count[e] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tile = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = at;
+      first_tile[e] = tile;
+      offsets[e] = at;
+      at += count[e];
+      tile += (count[e] + kExpertTile - 1) / kExpertTile;
+    }
+    first[experts] = at;
+    offsets[experts] = at;
+    tile_count[0] = tile;
+  }
+  __syncthreads();
+  for (int e = warp; e < experts; e += warps) {
+    int at = first[e];
+    for (int p = lane; p - lane < pairs; p += 32) {
+      const bool mine = p < pairs && ids[p] == e;
+      const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+      if (mine) order[at + __popc(ballot & ((1u << lane) - 1u))] = p;
+      at += __popc(ballot);
+    }
+    const int n = (count[e] + kExpertTile - 1) / kExpertTile;
+    for (int t = lane; t < n; t += 32) {
+      tiles[2 * (first_tile[e] + t)] = e;
+      tiles[2 * (first_tile[e] + t) + 1] = first[e] + t * kExpertTile;
+    }
+  }
+}
+
+__device__ __forceinline__ void load4(const float* p, float (&out)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&out)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+
+constexpr int kGroupedWarps = 8;
+constexpr int kGroupedPerWarp = 4;                               // outputs a warp computes for the tile's pairs
+constexpr int kGroupedChunk = 512;                               // inputs staged at a time
+
+// blockDim (32, kGroupedWarps); grid (tile slots, ceil(N / 32)).  The rows of a tile's pairs are staged in shared
+// memory 512 inputs at a time; a warp walks over a weight row with its lanes side by side (4 inputs a lane) and keeps
+// one sum per pair.  Every output is the same chain of partial sums and the same tree over the lanes whatever the
+// batch holds.  x row of sorted pair i: gather == null ? i : gather[i] / gather_div; out row: scatter == null ? i :
+// scatter[i].  GATED: out = silu(w_a x) * (w_b x), else out = w_a x.
+template <typename T, typename TO, bool GATED>
+__global__ void __launch_bounds__(kGroupedWarps * 32)
+moe_grouped_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ gather, int gather_div,
+                   const T* __restrict__ w_a, const T* __restrict__ w_b, TO* __restrict__ out, long long ldo,
+                   const int* __restrict__ scatter, const int* __restrict__ tiles, const int* __restrict__ tile_count,
+                   const int* __restrict__ offsets, int K, int N) {
+  __shared__ __align__(16) float rows[kExpertTile][kGroupedChunk];
+  __shared__ int source[kExpertTile];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  if ((int)blockIdx.x >= tile_count[0]) return;
+  const int lane = threadIdx.x, warp = threadIdx.y, thread = warp * 32 + lane;
+  const int expert = tiles[2 * blockIdx.x], start = tiles[2 * blockIdx.x + 1];
+  const int count = min(kExpertTile, offsets[expert + 1] - start);
+  if (thread < kExpertTile)
+    source[thread] = thread < count ? (gather != nullptr ? gather[start + thread] / gather_div : start + thread) : -1;
+  const int first_output = blockIdx.y * (kGroupedWarps * kGroupedPerWarp) + warp * kGroupedPerWarp;
+  float acc_a[kGroupedPerWarp][kExpertTile], acc_b[GATED ? kGroupedPerWarp : 1][kExpertTile];
+#pragma unroll
+  for (int j = 0; j < kGroupedPerWarp; ++j)
+#pragma unroll
+    for (int r = 0; r < kExpertTile; ++r) {
+      acc_a[j][r] = 0.0f;
+      if (GATED) acc_b[j][r] = 0.0f;
+    }
+  const bool wide = K % 4 == 0;
+  for (int from = 0; from < K; from += kGroupedChunk) {
+    const int here = min(kGroupedChunk, K - from);
+    __syncthreads();
+    for (int index = thread; index < kExpertTile * here; index += kGroupedWarps * 32) {
+      const int r = index / here, i = index - r * here;
+      rows[r][i] = source[r] >= 0 ? to_float(x[(size_t)source[r] * ldx + from + i]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kGroupedPerWarp; ++j) {
+      const int o = first_output + j;
+      if (o >= N) break;
+      const T* row_a = w_a + ((size_t)expert * N + o) * K + from;
+      const T* row_b = GATED ? w_b + ((size_t)expert * N + o) * K + from : nullptr;
+      if (wide) {
+        for (int i = lane * 4; i < here; i += 128) {
+          float a[4], b[4];
+          load4(row_a + i, a);
+          if (GATED) load4(row_b + i, b);
+#pragma unroll
+          for (int r = 0; r < kExpertTile; ++r) {
+            const float4 v = *reinterpret_cast<const float4*>(&rows[r][i]);
+            acc_a[j][r] = fmaf(a[3], v.w, fmaf(a[2], v.z, fmaf(a[1], v.y, fmaf(a[0], v.x, acc_a[j][r]))));
+            if (GATED) acc_b[j][r] = fmaf(b[3], v.w, fmaf(b[2], v.z, fmaf(b[1], v.y, fmaf(b[0], v.x, acc_b[j][r]))));
+          }
+        }
+      } else {
+        for (int i = lane; i < here; i += 32) {
+          const float a = to_float(row_a[i]);
+          const float b = GATED ? to_float(row_b[i]) : 0.0f;
+#pragma unroll
+          for (int r = 0; r < kExpertTile; ++r) {
+            acc_a[j][r] = fmaf(a, rows[r][i], acc_a[j][r]);
+            if (GATED) acc_b[j][r] = fmaf(b, rows[r][i], acc_b[j][r]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kGroupedPerWarp; ++j) {
+    const int o = first_output + j;
+#pragma unroll
+    for (int r = 0; r < kExpertTile; ++r) {
+      const float a = warp_sum(acc_a[j][r]);
+      const float b = GATED ? warp_sum(acc_b[j][r]) : 0.0f;
+      if (lane == r && r < count && o < N) {
+        const int to = scatter != nullptr ? scatter[start + r] : start + r;
+        const float value = GATED ? a / (1.0f + expf(-a)) * b : a;
+        out[(size_t)to * ldo + o] = from_float<TO>(value);
+      }
+    }
+  }
+}
+
+// One CTA per token: residual[t] += sum_s weights[t, s] * pair_rows[t * top + s] (+ shared_gate[t] * shared_rows[t], or
+// + shared_rows[t] without a gate), slots in their own order.
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ pair_rows,
+                                   const float* __restrict__ weights, const float* __restrict__ shared_rows,
+                                   const float* __restrict__ shared_gate, int width, int top) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int token = blockIdx.x;
+  const float gate = shared_rows != nullptr ? (shared_gate != nullptr ? shared_gate[token] : 1.0f) : 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float total = 0.0f;
+    for (int s = 0; s < top; ++s)
+      total = fmaf(weights[(size_t)token * top + s], pair_rows[((size_t)token * top + s) * width + c], total);
+    if (shared_rows != nullptr) total = fmaf(gate, shared_rows[(size_t)token * width + c], total);
+    residual[(size_t)token * width + c] += total;
+  }
+}
+
+template <typename T, typename TO, bool GATED>
+int launch_grouped(cudaStream_t stream, const void* x, long long ldx, const int* gather, int gather_div, const void* w_a,
+                   const void* w_b, void* out, long long ldo, const int* scatter, const int* tiles, const int* tile_count,
+                   const int* offsets, int pairs, int experts, int K, int N) {
+  const int slots = pairs / kExpertTile + experts;               // no more tiles than this, whatever the routing
+  const dim3 grid(slots, (N + kGroupedWarps * kGroupedPerWarp - 1) / (kGroupedWarps * kGroupedPerWarp));
+  return mir_launch(GATED ? "moe_grouped_gate_up" : "moe_grouped_down", moe_grouped_kernel<T, TO, GATED>, grid,
+                    dim3(32, kGroupedWarps), 0, stream, 0, (const T*)x, ldx, gather, gather_div, (const T*)w_a,
+                    (const T*)w_b, (TO*)out, ldo, scatter, tiles, tile_count, offsets, K, N);
+}
+
+}  // namespace
+
+// h [tokens, width] (row stride ld) in the activations' type; router [experts, width], correction [experts] (or
+// null), shared_gate_w [width] (or null) 32-bit; ids, weights [tokens, top]; shared_gate [tokens].
+MIR_EXPORT int mir_moe_route(int bf16, const void* h, long long ld, const float* router, const float* correction,
+                             const float* shared_gate_w, int* ids, float* weights, float* shared_gate, int tokens,
+                             int width, int experts, int top, int groups, int keep, float scale, cudaStream_t stream) {
+  if (tokens == 0) return MIR_OK;
+  if (tokens < 0 || width <= 0 || experts <= 0 || experts > kMaxExperts || top <= 0 || top > experts || groups <= 0 ||
+      experts % groups || keep <= 0 || keep > groups || (long long)keep * (experts / groups) < top) {
+    mir_set_error("moe_route: bad sizes (tokens %d, experts %d, top %d, groups %d of which %d are kept)", tokens, experts,
+                  top, groups, keep);
+    return MIR_BAD_ARGUMENT;
+  }
+  const size_t smem = (size_t)(2 * experts + groups) * sizeof(float);
+  if (bf16)
+    return mir_launch("moe_route", moe_route_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, stream, 0,
+                      (const __nv_bfloat16*)h, ld, router, correction, shared_gate_w, ids, weights, shared_gate, width,
+                      experts, top, groups, keep, scale);
+  return mir_launch("moe_route", moe_route_kernel<float>, dim3(tokens), dim3(128), smem, stream, 0, (const float*)h, ld,
+                    router, correction, shared_gate_w, ids, weights, shared_gate, width, experts, top, groups, keep, scale);
+}
+
+// How many ints `tiles` must hold for `pairs` pairs over `experts` experts.
+MIR_EXPORT int mir_moe_tile_slots(int pairs, int experts) { return pairs / kExpertTile + experts; }
+
+MIR_EXPORT int mir_moe_sort(const int* ids, int pairs, int experts, int* order, int* offsets, int* tiles, int* tile_count,
+                            cudaStream_t stream) {
+  if (pairs == 0) return MIR_OK;
+  if (pairs < 0 || experts <= 0 || experts > kMaxExperts) {
+    mir_set_error("moe_sort: bad sizes (pairs %d, experts %d)", pairs, experts);
+    return MIR_BAD_ARGUMENT;
+  }
+  return mir_launch("moe_sort", moe_sort_kernel, dim3(1), dim3(1024), 0, stream, 0, ids, pairs, experts, order, offsets,
+                    tiles, tile_count);
+}
+
+// hidden[i] = silu(w_gate[e] x) * (w_up[e] x) for the i-th sorted pair, x the row of its token (order[i] / top) of h.
+// w_gate, w_up [experts, inter, width]; hidden [pairs, inter] in the activations' type.
+MIR_EXPORT int mir_moe_gate_up(int bf16, const void* h, long long ld, const int* order, int top, const void* w_gate,
+                               const void* w_up, void* hidden, const int* tiles, const int* tile_count,
+                               const int* offsets, int pairs, int experts, int width, int inter, cudaStream_t stream) {
+  if (pairs == 0) return MIR_OK;
+  if (bf16)
+    return launch_grouped<__nv_bfloat16, __nv_bfloat16, true>(stream, h, ld, order, top, w_gate, w_up, hidden, inter,
+                                                              nullptr, tiles, tile_count, offsets, pairs, experts, width,
+                                                              inter);
+  return launch_grouped<float, float, true>(stream, h, ld, order, top, w_gate, w_up, hidden, inter, nullptr, tiles,
+                                            tile_count, offsets, pairs, experts, width, inter);
+}
+
+// pair_rows[order[i]] = w_down[e] hidden[i]: one 32-bit row [width] per pair, at the pair's own index.
+MIR_EXPORT int mir_moe_down(int bf16, const void* hidden, const int* order, const void* w_down, float* pair_rows,
+                            const int* tiles, const int* tile_count, const int* offsets, int pairs, int experts,
+                            int width, int inter, cudaStream_t stream) {
+  if (pairs == 0) return MIR_OK;
+  if (bf16)
+    return launch_grouped<__nv_bfloat16, float, false>(stream, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows,
+                                                       width, order, tiles, tile_count, offsets, pairs, experts, inter,
+                                                       width);
+  return launch_grouped<float, float, false>(stream, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows, width, order,
+                                             tiles, tile_count, offsets, pairs, experts, inter, width);
+}
+
+MIR_EXPORT int mir_moe_combine(float* residual, const float* pair_rows, const float* weights, const float* shared_rows,
+                               const float* shared_gate, int tokens, int width, int top, cudaStream_t stream) {
+  if (tokens == 0) return MIR_OK;
+  const int threads = width >= 1024 ? 256 : 128;
+  return mir_launch("moe_combine", moe_combine_kernel, dim3(tokens), dim3(threads), 0, stream, 0, residual, pair_rows,
+                    weights, shared_rows, shared_gate, width, top);
+}

@@ -33,7 +33,7 @@ _SIGNATURES = {
                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_paged_attention_generic": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                        c_int, c_void_p],
+                                        c_int, c_int, c_void_p],
         "mir_embed_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_longlong, c_longlong, c_float, c_void_p],
         "mir_gelu_tanh": [c_int, c_void_p, c_size_t, c_void_p],
@@ -47,7 +47,30 @@ _SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mir_delta_rule_set_lanes": [c_int],
         "mir_gated_head_norm": [c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int,
-                                c_float, c_int, c_void_p],
+                                c_float, c_int, c_int, c_void_p],
+        "mir_activation": [c_int, c_int, c_void_p, c_size_t, c_void_p],
+        "mir_softcap": [c_void_p, c_size_t, c_float, c_void_p],
+        "mir_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "mir_rms_norm_pair": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+        "mir_latent_prepare": [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                               c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
+        "mir_rope_rows": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
+                          c_float, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_head_linear": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p,
+                            c_longlong, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_wkv_mix": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_int, c_int, c_int, c_int, c_void_p],
+        "mir_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_moe_route": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                          c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "mir_moe_tile_slots": [c_int, c_int],
+        "mir_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "mir_moe_gate_up": [c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_moe_down": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_int, c_void_p],
+        "mir_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
         "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
@@ -459,17 +482,290 @@ def set_delta_rule_lanes(lanes: int) -> None:
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int,
                     value_dim: int, eps: float, sigmoid_gate: bool) -> None:
     """out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h]) per head, act = sigmoid or silu; o 32-bit
-    [tokens, heads * value_dim], gate a view with unit column stride in out's dtype or in float32, out contiguous."""
+    [tokens, heads * value_dim], gate a view with unit column stride in out's dtype or in float32, out contiguous.
+    The weight holds value_dim numbers (the same for every head) or heads * value_dim (a row per head)."""
     _cuda(o, gate, weight, out)
     tokens = o.shape[0]
     _require(o.dtype == torch.float32 and o.is_contiguous() and o.shape[1] == heads * value_dim
              and gate.shape == o.shape and gate.stride(1) == 1 and out.shape == o.shape and out.is_contiguous()
              and gate.dtype in (out.dtype, torch.float32) and weight.dtype == torch.float32
-             and weight.numel() == value_dim, "gated_head_norm: shapes or dtypes do not fit")
+             and weight.numel() in (value_dim, heads * value_dim) and weight.is_contiguous(),
+             "gated_head_norm: shapes or dtypes do not fit")
     lib = library("core")
     _check(lib, lib.mir_gated_head_norm(_is_bf16(out), int(gate.dtype == torch.float32), o.data_ptr(), gate.data_ptr(),
                                         gate.stride(0), weight.data_ptr(),
-                                        out.data_ptr(), tokens, heads, value_dim, eps, int(sigmoid_gate), _stream()))
+                                        out.data_ptr(), tokens, heads, value_dim, eps, int(sigmoid_gate),
+                                        int(heads > 1 and weight.numel() == heads * value_dim), _stream()))
+
+
+def gelu_erf(x: torch.Tensor) -> None:
+    """x <- 0.5 x (1 + erf(x / sqrt 2)) in place, computed in 32-bit."""
+    _cuda(x)
+    _require(x.is_contiguous(), "gelu_erf: a contiguous tensor is needed")
+    lib = library("core")
+    _check(lib, lib.mir_activation(1, _is_bf16(x), x.data_ptr(), x.numel(), _stream()))
+
+
+def tanh(x: torch.Tensor) -> None:
+    """x <- tanh(x) in place, computed in 32-bit."""
+    _cuda(x)
+    _require(x.is_contiguous(), "tanh: a contiguous tensor is needed")
+    lib = library("core")
+    _check(lib, lib.mir_activation(2, _is_bf16(x), x.data_ptr(), x.numel(), _stream()))
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap) in place on contiguous 32-bit logits."""
+    _cuda(logits)
+    _require(logits.dtype == torch.float32 and logits.is_contiguous(), "softcap: contiguous float32 logits are needed")
+    lib = library("core")
+    _check(lib, lib.mir_softcap(logits.data_ptr(), logits.numel(), float(cap), _stream()))
+
+
+def add_rows(residual: torch.Tensor, rows: Optional[torch.Tensor], vector: Optional[torch.Tensor]) -> None:
+    """residual[r] += rows[r] + vector on the 32-bit residual stream (either may be None)."""
+    _cuda(residual, rows, vector)
+    n, hidden = residual.shape
+    _require(residual.dtype == torch.float32 and residual.is_contiguous()
+             and (rows is None or (rows.dtype == torch.float32 and rows.shape == residual.shape and rows.is_contiguous()))
+             and (vector is None or (vector.dtype == torch.float32 and vector.numel() == hidden and vector.is_contiguous())),
+             "add_rows: float32 rows of the residual's shape and a float32 vector of its width")
+    if rows is None and vector is None:
+        return
+    lib = library("core")
+    _check(lib, lib.mir_add_rows(residual.data_ptr(), _ptr(rows), _ptr(vector), n, hidden, _stream()))
+
+
+def rms_norm_pair(x: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float, out_a: torch.Tensor,
+                  out_b: torch.Tensor) -> None:
+    """out_a = rmsnorm(x) * weight_a and out_b = rmsnorm(x) * weight_b in one pass over the 32-bit rows x."""
+    _cuda(x, weight_a, weight_b, out_a, out_b)
+    rows, hidden = x.shape
+    _require(x.dtype == torch.float32 and x.is_contiguous() and out_a.shape == x.shape and out_b.shape == x.shape
+             and out_a.is_contiguous() and out_b.is_contiguous() and out_a.dtype == out_b.dtype
+             and all(w.dtype == torch.float32 and w.numel() == hidden and w.is_contiguous() for w in (weight_a, weight_b)),
+             "rms_norm_pair: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_rms_norm_pair(_is_bf16(out_a), x.data_ptr(), weight_a.data_ptr(), weight_b.data_ptr(),
+                                      out_a.data_ptr(), out_b.data_ptr(), rows, hidden, eps, _stream()))
+
+
+# --------------------------------------------------------------------------- latent attention
+def latent_prepare(packed: torch.Tensor, q_offset: int, q_rank: int, kv_offset: int, kv_rank: int, rotary_dim: int,
+                   q_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float, positions: torch.Tensor,
+                   slot_mapping: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], magnitude: float,
+                   interleaved: bool, latent_q: torch.Tensor, pages: Optional[torch.Tensor]) -> None:
+    """Per token of the packed projection `packed` [tokens, >= offsets + widths]: latent_q = rmsnorm(packed[q_offset :
+    + q_rank]) * q_norm; the token's cache row pages[slot] = [rmsnorm(packed[kv_offset : + kv_rank]) * kv_norm | the
+    rotary_dim columns behind it rotated by the token's position].  Norms and angles are 32-bit.  A token whose slot
+    is negative (or with slot_mapping None) writes no cache row."""
+    _cuda(packed, q_norm, kv_norm, positions, slot_mapping, inv_freq, latent_q, pages)
+    tokens = packed.shape[0]
+    _require(packed.stride(1) == 1 and q_offset + q_rank <= packed.shape[1]
+             and kv_offset + kv_rank + rotary_dim <= packed.shape[1] and latent_q.dtype == packed.dtype
+             and latent_q.is_contiguous() and latent_q.shape == (tokens, q_rank)
+             and q_norm.dtype == torch.float32 and q_norm.numel() == q_rank and kv_norm.dtype == torch.float32
+             and kv_norm.numel() == kv_rank and positions.dtype == torch.int32 and positions.numel() >= tokens,
+             "latent_prepare: shapes or dtypes do not fit")
+    if slot_mapping is not None:
+        _require(slot_mapping.dtype == torch.int32 and pages is not None and pages.dtype == packed.dtype
+                 and pages.is_contiguous() and pages[0].numel() == kv_rank + rotary_dim,
+                 "latent_prepare: cache rows of kv_rank + rotary_dim elements in the activations' dtype are needed")
+    if rotary_dim:
+        _require(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+                 "latent_prepare: the angle table must hold rotary_dim / 2 float32 values")
+    lib = library("core")
+    _check(lib, lib.mir_latent_prepare(_is_bf16(packed), packed.data_ptr(), packed.stride(0), q_offset, q_rank, kv_offset,
+                                       kv_rank, rotary_dim, q_norm.data_ptr(), kv_norm.data_ptr(), eps,
+                                       positions.data_ptr(), _ptr(slot_mapping), _ptr(inv_freq), float(magnitude),
+                                       int(interleaved), latent_q.data_ptr(), _ptr(pages), tokens, _stream()))
+
+
+def rope_rows(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, magnitude: float,
+              interleaved: bool) -> None:
+    """dst[t, h, :r] = src[t, h, :r] rotated by positions[t], r = 2 * len(inv_freq): pairs (i, i + r/2) or, interleaved,
+    (2i, 2i + 1); cos and sin times `magnitude`; angles are 32-bit.  src and dst are [tokens, heads, >= r] views with
+    unit stride in the last dimension and may be the same tensor."""
+    _cuda(src, dst, positions, inv_freq)
+    tokens, heads = src.shape[0], src.shape[1]
+    rotary = 2 * inv_freq.numel()
+    _require(src.dim() == 3 and dst.dim() == 3 and dst.shape[:2] == src.shape[:2] and src.stride(2) == 1
+             and dst.stride(2) == 1 and src.shape[2] >= rotary and dst.shape[2] >= rotary and src.dtype == dst.dtype
+             and positions.dtype == torch.int32 and positions.numel() >= tokens and inv_freq.dtype == torch.float32,
+             "rope_rows: [tokens, heads, dims] views of one dtype are needed")
+    lib = library("core")
+    _check(lib, lib.mir_rope_rows(_is_bf16(src), src.data_ptr(), src.stride(0), src.stride(1), dst.data_ptr(),
+                                  dst.stride(0), dst.stride(1), positions.data_ptr(), inv_freq.data_ptr(),
+                                  float(magnitude), int(interleaved), tokens, heads, rotary, _stream()))
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, :] = weight[h]^T x[t, h, :] for weight [heads, in, out] (a product per head; 32-bit accumulation),
+    times sigmoid(gate[t, h, :]) if a gate [tokens, heads * out] (unit column stride) is given.  x [tokens, heads, in]
+    and out [tokens, heads, out] are views with unit stride in the last dimension."""
+    _cuda(x, weight, out, gate)
+    tokens, heads, in_dim = x.shape
+    out_dim = weight.shape[2]
+    _require(weight.shape == (heads, in_dim, out_dim) and weight.is_contiguous() and out.shape == (tokens, heads, out_dim)
+             and x.stride(2) == 1 and out.stride(2) == 1 and x.dtype == weight.dtype == out.dtype,
+             "head_linear: x [tokens, heads, in], weight [heads, in, out], out [tokens, heads, out] of one dtype")
+    if gate is not None:
+        _require(gate.shape == (tokens, heads * out_dim) and gate.stride(1) == 1 and gate.dtype == x.dtype,
+                 "head_linear: the gate is [tokens, heads * out] in the activations' dtype")
+    lib = library("core")
+    _check(lib, lib.mir_head_linear(_is_bf16(x), x.data_ptr(), x.stride(0), x.stride(1), weight.data_ptr(), out.data_ptr(),
+                                    out.stride(0), out.stride(1), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                    tokens, heads, in_dim, out_dim, _stream()))
+
+
+# --------------------------------------------------------------------------- wkv
+def wkv_mix(h: torch.Tensor, tail: torch.Tensor, mu: torch.Tensor, row_of_token: torch.Tensor,
+            query_starts: torch.Tensor, state_slots: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+            single_tokens_only: bool = False) -> None:
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s] for the five mixes s; h[t - 1] of a portion's first token is the
+    request's tail [slots, width] (32-bit; zeros at its start), which moves on to the portion's last row.
+    `single_tokens_only`: every request brings one token (the tails then move on inside the one kernel)."""
+    _cuda(h, tail, mu, row_of_token, query_starts, state_slots, positions, out)
+    tokens, width = h.shape
+    rows = query_starts.numel() - 1
+    _require(h.stride(1) == 1 and tail.dtype == torch.float32 and tail.is_contiguous() and tail.shape[1] == width
+             and mu.dtype == torch.float32 and mu.is_contiguous() and mu.shape == (5, width)
+             and out.dtype == h.dtype and out.is_contiguous() and out.shape == (5, tokens, width),
+             "wkv_mix: shapes or dtypes do not fit")
+    _require(all(t.dtype == torch.int32 for t in (row_of_token, query_starts, state_slots, positions)),
+             "wkv_mix: the batch description is int32")
+    lib = library("core")
+    _check(lib, lib.mir_wkv_mix(_is_bf16(h), h.data_ptr(), h.stride(0), tail.data_ptr(), mu.data_ptr(),
+                                row_of_token.data_ptr(), query_starts.data_ptr(), state_slots.data_ptr(),
+                                positions.data_ptr(), out.data_ptr(), tokens, rows, width, int(single_tokens_only),
+                                _stream()))
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_raw: torch.Tensor, decay_bias: torch.Tensor,
+             bonus: torch.Tensor, state: torch.Tensor, query_starts: torch.Tensor, state_slots: torch.Tensor,
+             positions: torch.Tensor, out: torch.Tensor, heads: int, dim: int) -> None:
+    """The wkv recurrence over the tokens of each request row, from and into state [slots, heads, dim (value channel),
+    dim (key channel)] (32-bit): per head o = S^T r + (sum_i r_i u_i k_i) v; S <- diag(w) S + k v^T with
+    w = exp(-exp(decay_raw + decay_bias)).  r, k, v [tokens, heads * dim] (one row stride, the activations' dtype);
+    decay_raw 32-bit [tokens, heads * dim]; decay_bias, bonus (u) 32-bit [heads * dim]; out 32-bit [tokens, heads * dim]."""
+    _cuda(r, k, v, decay_raw, decay_bias, bonus, state, query_starts, state_slots, positions, out)
+    tokens = r.shape[0]
+    rows = query_starts.numel() - 1
+    width = heads * dim
+    _require(all(t.shape == (tokens, width) and t.stride(1) == 1 and t.stride(0) == r.stride(0) and t.dtype == r.dtype
+                 for t in (r, k, v)), "wkv_scan: r, k, v are [tokens, heads * dim] with one row stride and dtype")
+    _require(decay_raw.dtype == torch.float32 and decay_raw.is_contiguous() and decay_raw.shape == (tokens, width)
+             and out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, width)
+             and all(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == width for t in (decay_bias, bonus))
+             and state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, dim, dim),
+             "wkv_scan: decays, bonus, state and out are contiguous float32 of the stated shapes")
+    lib = library("core")
+    _check(lib, lib.mir_wkv_scan(_is_bf16(r), r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0), decay_raw.data_ptr(),
+                                 decay_bias.data_ptr(), bonus.data_ptr(), state.data_ptr(), query_starts.data_ptr(),
+                                 state_slots.data_ptr(), positions.data_ptr(), out.data_ptr(), tokens, rows, heads, dim,
+                                 _stream()))
+
+
+# --------------------------------------------------------------------------- routed experts
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor],
+              shared_gate_weight: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor,
+              shared_gate: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float) -> None:
+    """Per token: scores = sigmoid(router h) in 32-bit; the `top` experts with the largest score + correction among
+    the experts of the `keep` best of `groups` groups of neighbours (a group's score: the sum of its two largest
+    score + correction) -> ids [tokens, top]; weights [tokens, top] = their scores / their sum * scale;
+    shared_gate[t] = sigmoid(shared_gate_weight . h) if given."""
+    _cuda(h, router, correction, shared_gate_weight, ids, weights, shared_gate)
+    tokens, width = h.shape
+    experts = router.shape[0]
+    _require(h.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == width
+             and (correction is None or (correction.dtype == torch.float32 and correction.numel() == experts))
+             and ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (tokens, top)
+             and weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == (tokens, top),
+             "moe_route: shapes or dtypes do not fit")
+    if shared_gate_weight is not None:
+        _require(shared_gate_weight.dtype == torch.float32 and shared_gate_weight.numel() == width
+                 and shared_gate_weight.is_contiguous() and shared_gate is not None and shared_gate.dtype == torch.float32
+                 and shared_gate.numel() >= tokens, "moe_route: the shared gate is a float32 vector of the width")
+    lib = library("core")
+    _check(lib, lib.mir_moe_route(_is_bf16(h), h.data_ptr(), h.stride(0), router.data_ptr(), _ptr(correction),
+                                  _ptr(shared_gate_weight), ids.data_ptr(), weights.data_ptr(), _ptr(shared_gate), tokens,
+                                  width, experts, top, groups, keep, float(scale), _stream()))
+
+
+class ExpertOrder:
+    """The pairs (token, chosen expert) of a step ordered by expert, on the device: order [pairs] (sorted place ->
+    pair), offsets [experts + 1], tiles [2 * slots] and tile_count [1] for the grouped products."""
+
+    def __init__(self, alloc, pairs: int, experts: int):
+        lib = library("core")
+        slots = int(lib.mir_moe_tile_slots(pairs, experts))
+        self.pairs, self.experts = pairs, experts
+        self.order = alloc((pairs,), torch.int32)
+        self.offsets = alloc((experts + 1,), torch.int32)
+        self.tiles = alloc((2 * slots,), torch.int32)
+        self.tile_count = alloc((1,), torch.int32)
+
+
+def moe_sort(ids: torch.Tensor, experts: int, alloc) -> ExpertOrder:
+    """Order the pairs of ids [tokens, top] by expert (a pair's place among its expert's pairs follows its index)."""
+    _cuda(ids)
+    _require(ids.dtype == torch.int32 and ids.is_contiguous(), "moe_sort: contiguous int32 ids are needed")
+    found = ExpertOrder(alloc, ids.numel(), experts)
+    lib = library("core")
+    _check(lib, lib.mir_moe_sort(ids.data_ptr(), ids.numel(), experts, found.order.data_ptr(), found.offsets.data_ptr(),
+                                 found.tiles.data_ptr(), found.tile_count.data_ptr(), _stream()))
+    return found
+
+
+def moe_gate_up(h: torch.Tensor, found: ExpertOrder, top: int, w_gate: torch.Tensor, w_up: torch.Tensor,
+                hidden: torch.Tensor) -> None:
+    """hidden[i] = silu(w_gate[e] x) * (w_up[e] x) for the i-th pair in expert order, x its token's row of h and e its
+    expert; w_gate, w_up [experts, inter, width]; hidden [pairs, inter]."""
+    _cuda(h, w_gate, w_up, hidden)
+    tokens, width = h.shape
+    experts, inter = w_gate.shape[0], w_gate.shape[1]
+    _require(h.stride(1) == 1 and w_gate.shape == (experts, inter, width) and w_up.shape == w_gate.shape
+             and w_gate.is_contiguous() and w_up.is_contiguous() and hidden.is_contiguous()
+             and hidden.shape == (found.pairs, inter) and found.pairs == tokens * top and found.experts == experts
+             and h.dtype == w_gate.dtype == w_up.dtype == hidden.dtype, "moe_gate_up: shapes or dtypes do not fit")
+    lib = library("core")
+    _check(lib, lib.mir_moe_gate_up(_is_bf16(h), h.data_ptr(), h.stride(0), found.order.data_ptr(), top,
+                                    w_gate.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), found.tiles.data_ptr(),
+                                    found.tile_count.data_ptr(), found.offsets.data_ptr(), found.pairs, experts, width,
+                                    inter, _stream()))
+
+
+def moe_down(hidden: torch.Tensor, found: ExpertOrder, w_down: torch.Tensor, pair_rows: torch.Tensor) -> None:
+    """pair_rows[pair] = w_down[e] hidden[i] (32-bit [pairs, width]) for the i-th pair in expert order."""
+    _cuda(hidden, w_down, pair_rows)
+    experts, width, inter = w_down.shape
+    _require(hidden.is_contiguous() and hidden.shape == (found.pairs, inter) and w_down.is_contiguous()
+             and hidden.dtype == w_down.dtype and pair_rows.dtype == torch.float32 and pair_rows.is_contiguous()
+             and pair_rows.shape == (found.pairs, width) and found.experts == experts,
+             "moe_down: shapes or dtypes do not fit")
+    lib = library("core")
+    _check(lib, lib.mir_moe_down(_is_bf16(hidden), hidden.data_ptr(), found.order.data_ptr(), w_down.data_ptr(),
+                                 pair_rows.data_ptr(), found.tiles.data_ptr(), found.tile_count.data_ptr(),
+                                 found.offsets.data_ptr(), found.pairs, experts, width, inter, _stream()))
+
+
+def moe_combine(residual: torch.Tensor, pair_rows: torch.Tensor, weights: torch.Tensor,
+                shared_rows: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor]) -> None:
+    """residual[t] += sum_s weights[t, s] * pair_rows[t * top + s] + shared_gate[t] * shared_rows[t] (the gate 1 if
+    None; nothing of it without shared_rows); all 32-bit."""
+    _cuda(residual, pair_rows, weights, shared_rows, shared_gate)
+    tokens, width = residual.shape
+    top = weights.shape[1]
+    _require(residual.dtype == torch.float32 and residual.is_contiguous() and pair_rows.dtype == torch.float32
+             and pair_rows.is_contiguous() and pair_rows.shape == (tokens * top, width) and weights.dtype == torch.float32
+             and weights.is_contiguous() and weights.shape[0] == tokens
+             and (shared_rows is None or (shared_rows.dtype == torch.float32 and shared_rows.is_contiguous()
+                                          and shared_rows.shape == residual.shape))
+             and (shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.numel() >= tokens)),
+             "moe_combine: shapes or dtypes do not fit")
+    lib = library("core")
+    _check(lib, lib.mir_moe_combine(residual.data_ptr(), pair_rows.data_ptr(), weights.data_ptr(), _ptr(shared_rows),
+                                    _ptr(shared_gate), tokens, width, top, _stream()))
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -586,10 +882,14 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
                             page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
-                            window: Optional[int], value_dim: Optional[int] = None, keep_first: int = 0) -> None:
+                            window: Optional[int], value_dim: Optional[int] = None, keep_first: int = 0,
+                            values_in_keys: bool = False) -> None:
     """out[t, h] = softmax over the visible cached keys of token t's request; q is read from the packed qkv rows.
     `value_dim`: width of a value head (head_dim if None); `keep_first`: with a window, the request's first keys
-    that stay visible to every query."""
+    that stay visible to every query; `values_in_keys`: a value is the first value_dim elements of its key (a cached
+    latent that is read both ways) and v_pages is not looked at."""
+    if values_in_keys:
+        v_pages = k_pages
     _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions)
     tokens = out.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
@@ -601,7 +901,8 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
     _check(lib, lib.mir_paged_attention_generic(
         _is_bf16(out), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], row_of_token.data_ptr(), positions.data_ptr(), tokens,
-        page_size, heads, kv_heads, head_dim, value_dim, scale, int(window or 0), int(keep_first or 0), _stream()))
+        page_size, heads, kv_heads, head_dim, value_dim, scale, int(window or 0), int(keep_first or 0),
+        head_dim if values_in_keys else 0, _stream()))
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel

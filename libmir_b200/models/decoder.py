@@ -40,6 +40,7 @@ class DecoderModel:
         self.final_norm = build_part(spec.final_norm, env)
         self.embedding: Optional[torch.Tensor] = None
         self.pair_embedding: Optional[torch.Tensor] = None      # the table of token pairs, if the model has one
+        self.loop_steps: Optional[torch.Tensor] = None          # [passes, hidden] 32-bit: what each pass of a loop adds
         self.head: Optional[torch.Tensor] = None
         self._runs_key, self._runs_list, self._native = None, [], {}
 
@@ -67,6 +68,9 @@ class DecoderModel:
         if spec.embedding.pairs is not None:
             pairs = spec.embedding.pairs
             table[pairs.name] = (self, "pair_embedding", ParamSpec((pairs.buckets + 1, spec.embedding.hidden_size)))
+        if spec.loop is not None and spec.loop.step_tensor:
+            table[spec.loop.step_tensor] = (self, "loop_steps", ParamSpec((spec.loop.passes, spec.hidden_size), init="zeros",
+                                                                          store="float32", accept_transposed=False))
         for layer_spec, block in zip(spec.layers, self.blocks):
             for slot, part in block.parts():
                 for local, param in part.parameters().items():
@@ -89,6 +93,8 @@ class DecoderModel:
                 if "pair_embedding" in local_tensors:
                     self.pair_embedding = local_tensors["pair_embedding"].contiguous()
                 self.head = local_tensors.get("head")
+                if "loop_steps" in local_tensors:
+                    self.loop_steps = local_tensors["loop_steps"].contiguous()
             else:
                 owner.bind(local_tensors)
         if self.spec.head.tied:
@@ -122,6 +128,15 @@ class DecoderModel:
         total += self.final_norm.weight_bytes() + self.head.numel() * self.head.element_size()
         return total
 
+    def open_pass(self, ctx, entry, residual: torch.Tensor, embedded: Optional[torch.Tensor]) -> None:
+        """What a pass of the model's loop starts with: every pass but the first adds the embedding's output to the
+        residual, every pass adds its row of the step tensor."""
+        loop = self.spec.loop
+        rows = embedded if (loop.add_embedding and entry.opens_pass > 0) else None
+        vector = self.loop_steps[entry.opens_pass] if self.loop_steps is not None else None
+        kernels.add_rows(residual, rows, vector)
+        ctx.residual_stats = None
+
     # -- running --------------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
         """Run the tokens of the step; returns the 32-bit residual [T, H] after the last layer."""
@@ -133,17 +148,24 @@ class DecoderModel:
                                 pairs.mul_previous, pairs.mul_current, spec.embedding.multiplier)
         else:
             kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
+        embedded = None
+        if spec.loop is not None and spec.loop.add_embedding and any((e.opens_pass or 0) > 0 for e in spec.schedule):
+            embedded = ctx.alloc(tuple(residual.shape), torch.float32)       # later passes add the embedding's output again
+            embedded.copy_(residual)
         for run in self._runs(ctx):
             if run.layers is not None:
                 run.execute(ctx, residual)
                 continue
             index = run.first
             entry = spec.schedule[index]
+            if entry.opens_pass is not None:
+                self.open_pass(ctx, entry, residual, embedded)
             # the norm that the next block in the schedule starts with: this block's last product may prepare it
             following = self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None
             ctx.norm_after_block = following.first_norm() if following is not None else None
-            if index + 1 < len(spec.schedule) and self._native.get(index + 1) is not None:
-                ctx.norm_after_block = None          # the executor that runs the next block starts from the residual
+            if index + 1 < len(spec.schedule) and (self._native.get(index + 1) is not None
+                                                   or spec.schedule[index + 1].opens_pass is not None):
+                ctx.norm_after_block = None          # the next block starts from a residual that this one has not seen
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), residual)
         return residual
 
@@ -158,7 +180,8 @@ class DecoderModel:
         self._native = {}
         if kernels.NATIVE_LAYERS:
             for index, entry in enumerate(self.spec.schedule):
-                self._native[index] = self.blocks[entry.layer].native_descriptor(ctx.cache_view(index))
+                self._native[index] = self.blocks[entry.layer].native_descriptor(ctx.cache_view(index)) \
+                    if entry.opens_pass is None else None        # (a pass opens from Python, before its first block)
         runs, index = [], 0
         while index < len(self.spec.schedule):
             if self._native.get(index) is None:
@@ -181,4 +204,8 @@ class DecoderModel:
         if out is None:
             out = ctx.alloc((rows.numel(), self.spec.vocab_size), torch.float32)
         kernels.head_logits(normed, self.head, out, candidates)
+        if self.spec.head.softcap:
+            kernels.softcap(out, self.spec.head.softcap)
+            if candidates is not None:
+                candidates.valid = False             # (they hold the logits as they were before the cap)
         return out

@@ -5,7 +5,10 @@ from .attention import SoftmaxAttention
 from .base import Block, BuildEnv, FeedForward, Mixer, Norm, Part, PartContext, Position, ScratchContext
 from .block import ARRANGEMENTS, ParallelBlock, PreNormBlock, build_block
 from .delta_rule import GatedDeltaRule
+from .experts import RoutedExperts
 from .feed_forward import GeluMlp, SwiGlu
+from .latent_attention import LatentAttention
+from .wkv import Wkv
 from .side_by_side import SideBySide
 from .norm import RmsNorm
 from .rope import Rotary, inverse_frequencies
@@ -17,7 +20,10 @@ register_part("swiglu", SwiGlu)
 register_part("gelu_mlp", GeluMlp)
 register_part("gated_delta_rule", GatedDeltaRule)
 register_part("side_by_side", SideBySide)
+register_part("latent_attention", LatentAttention)
+register_part("wkv", Wkv)
+register_part("routed_experts", RoutedExperts)
 
-__all__ = ["ARRANGEMENTS", "Block", "BuildEnv", "FeedForward", "GatedDeltaRule", "GeluMlp", "Mixer", "Norm", "ParallelBlock", "Part",
-           "PartContext", "Position", "PreNormBlock", "RmsNorm", "Rotary", "ScratchContext", "SideBySide", "SoftmaxAttention",
-           "SwiGlu", "build_block", "inverse_frequencies"]
+__all__ = ["ARRANGEMENTS", "Block", "BuildEnv", "FeedForward", "GatedDeltaRule", "GeluMlp", "LatentAttention", "Mixer", "Norm",
+           "ParallelBlock", "Part", "PartContext", "Position", "PreNormBlock", "RmsNorm", "Rotary", "RoutedExperts",
+           "ScratchContext", "SideBySide", "SoftmaxAttention", "SwiGlu", "Wkv", "build_block", "inverse_frequencies"]

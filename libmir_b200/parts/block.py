@@ -8,6 +8,9 @@ A layer without feed-forward, or without one of the norms, leaves that step out.
 parallel:  h = norm_1(x);  x += mixer(h) + feed_forward(h)
 One norm, and both branches read its output; each adds its result into the 32-bit residual, so the sum
 x + mixer(h) + feed_forward(h) is formed in 32-bit whatever the engine's dtype.
+With a second norm (`feed_forward_norm`): x += mixer(norm_1(x)) + feed_forward(norm_2(x)), both norms of the same x:
+both are computed before either branch adds into the residual, by one kernel where they are RMS norms with one eps
+(one root mean square, two weights).
 """
 
 from __future__ import annotations
@@ -105,16 +108,18 @@ class PreNormBlock(Block):
 
 
 class ParallelBlock(Block):
-    """x += mixer(norm(x)) + feed_forward(norm(x)): the norm runs once and both branches read its output."""
+    """x += mixer(norm(x)) + feed_forward(norm(x)): the norm runs once and both branches read its output; or, with a
+    second norm, x += mixer(norm_1(x)) + feed_forward(norm_2(x)) with both norms taken of the same x."""
 
-    SLOTS = ("mixer_norm", "mixer", "feed_forward")
+    SLOTS = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
-        if spec.feed_forward_norm is not None:
-            raise ValueError("the parallel arrangement has one norm: feed_forward_norm must be None")
+        if spec.feed_forward_norm is not None and (spec.feed_forward is None or spec.mixer_norm is None):
+            raise ValueError("a second norm in the parallel arrangement needs a feed-forward and a first norm")
         self.mixer_norm = build_part(spec.mixer_norm, env)
         self.mixer = build_part(spec.mixer, env)
+        self.feed_forward_norm = build_part(spec.feed_forward_norm, env)
         self.feed_forward = build_part(spec.feed_forward, env)
 
     def parts(self):
@@ -124,13 +129,16 @@ class ParallelBlock(Block):
         return self.mixer.cache_requirement()
 
     def first_norm(self):
-        return self.mixer_norm
+        return self.mixer_norm if self.feed_forward_norm is None else None    # (two norms run as one kernel of their own)
 
     def forward(self, ctx, cache, residual):
         # Both branches read the same normed rows.  If the product that last added into the residual left what this
         # norm needs (sums of squares and weighted rows: a few-rows step), and both branches can take the norm over
         # into their first products, no norm kernel runs; else the norm runs once as a kernel.
         after = ctx.norm_after_block
+        if self.feed_forward_norm is not None:
+            self._forward_two_norms(ctx, cache, residual, after)
+            return
         consumers = [part for part in (self.mixer, self.feed_forward) if part is not None]
         foldable = self.mixer_norm is not None and self.mixer_norm.foldable and \
             all(part.takes_normed_residual for part in consumers)
@@ -146,6 +154,27 @@ class ParallelBlock(Block):
             ctx.residual_stats = None
             ctx.upcoming_norm = after
             self.feed_forward.forward(ctx, x, residual)
+        ctx.upcoming_norm = None
+
+
+    def _forward_two_norms(self, ctx, cache, residual, after):
+        """Both norms read the residual as it is now, so both run before either branch adds into it."""
+        from .norm import RmsNorm
+        first, second = self.mixer_norm, self.feed_forward_norm
+        if type(first) is RmsNorm and type(second) is RmsNorm and first.spec.eps == second.spec.eps \
+                and first.spec.size == second.spec.size:
+            from .. import kernels
+            shape = (residual.shape[0], first.spec.size)
+            x_mixer, x_feed = ctx.alloc(shape, self.env.dtype), ctx.alloc(shape, self.env.dtype)
+            kernels.rms_norm_pair(residual, first.weight, second.weight, first.spec.eps, x_mixer, x_feed)
+        else:
+            x_mixer, x_feed = first.forward(ctx, residual), second.forward(ctx, residual)
+        ctx.residual_stats = None
+        ctx.upcoming_norm = None
+        self.mixer.forward(ctx, cache, x_mixer, residual)
+        ctx.residual_stats = None
+        ctx.upcoming_norm = after
+        self.feed_forward.forward(ctx, x_feed, residual)
         ctx.upcoming_norm = None
 
 

@@ -1,0 +1,94 @@
+"""A mixture of gated experts with a routed choice per token, and an optional shared expert.
+
+With h the feed-forward's input, E experts of which each token uses `top`:
+    s = sigmoid(W_router h)                        32-bit
+    choice = s + correction                        the correction steers the choice only
+    a group = E / groups neighbouring experts; its score = the sum of its two largest choice scores; only experts
+    of the `keep_groups` best groups can be chosen (the others count as minus infinity)
+    chosen = the `top` experts with the largest choice scores;  weight = s[chosen] / (sum of them + 1e-20) * scale
+    out = sum over chosen of weight * expert(h)    expert(h) = W_down (silu(W_gate h) * (W_up h))
+        + sigmoid(w_sg . h) * shared(h)            one number per token gates the shared expert, if there is one
+Everything runs on the device without a count ever being read back (csrc/moe.cu): the (token, expert) pairs are
+ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights, and one kernel
+adds the weighted rows, and the shared expert's, into the 32-bit residual.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..config.spec import ParamSpec
+from .base import FeedForward
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        s = spec
+        if s.experts <= 0 or not 0 < s.top <= s.experts or s.groups <= 0 or s.experts % s.groups \
+                or not 0 < s.keep_groups <= s.groups or s.keep_groups * (s.experts // s.groups) < s.top:
+            raise ValueError(f"routed experts: {s.top} of {s.experts} experts cannot be chosen from {s.keep_groups} of "
+                             f"{s.groups} groups")
+        self.router = self.correction = self.w_gate = self.w_up = self.w_down = None
+        self.shared_gate_up = self.shared_down = self.shared_gate = None
+
+    def parameters(self):
+        s = self.spec
+        matrix = lambda rows, columns: ParamSpec((rows, columns), accept_transposed=False)
+        table = {"router": ParamSpec((s.experts, s.hidden_size), store="float32", accept_transposed=False)}
+        if s.correction:
+            table["correction"] = ParamSpec((s.experts,), init="zeros", store="float32")
+        for expert in range(s.experts):
+            table[f"e{expert}.gate"] = matrix(s.expert_size, s.hidden_size)
+            table[f"e{expert}.up"] = matrix(s.expert_size, s.hidden_size)
+            table[f"e{expert}.down"] = matrix(s.hidden_size, s.expert_size)
+        if s.shared_size:
+            table["shared.gate"] = matrix(s.shared_size, s.hidden_size)
+            table["shared.up"] = matrix(s.shared_size, s.hidden_size)
+            table["shared.down"] = matrix(s.hidden_size, s.shared_size)
+            if s.shared_gate:
+                table["shared.sg"] = ParamSpec((1, s.hidden_size), store="float32", accept_transposed=False)
+        return table
+
+    def bind(self, tensors):
+        s = self.spec
+        self.router = tensors["router"].contiguous()
+        self.correction = tensors["correction"].contiguous() if s.correction else None
+        stack = lambda name: torch.stack([tensors[f"e{expert}.{name}"] for expert in range(s.experts)]).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        if s.shared_size:
+            self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0)
+            self.shared_down = tensors["shared.down"].contiguous()
+            self.shared_gate = tensors["shared.sg"].reshape(-1).contiguous() if s.shared_gate else None
+
+    def weight_bytes(self):
+        """What a step reads at most: the router, the shared expert, and `top` experts per token would be the least; a
+        large batch reads every expert."""
+        tensors = (self.router, self.w_gate, self.w_up, self.w_down, self.shared_gate_up, self.shared_down)
+        return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+    def forward(self, ctx, x, residual):
+        s = self.spec
+        tokens = x.shape[0]
+        dtype = self.env.dtype
+        ids = ctx.alloc((tokens, s.top), torch.int32)
+        weights = ctx.alloc((tokens, s.top), torch.float32)
+        gate = ctx.alloc((tokens,), torch.float32) if self.shared_gate is not None else None
+        kernels.moe_route(x, self.router, self.correction, self.shared_gate, ids, weights, gate, s.top, s.groups,
+                          s.keep_groups, s.scale)
+        found = kernels.moe_sort(ids, s.experts, ctx.alloc)
+        hidden = ctx.alloc((tokens * s.top, s.expert_size), dtype)
+        kernels.moe_gate_up(x, found, s.top, self.w_gate, self.w_up, hidden)
+        pair_rows = ctx.alloc((tokens * s.top, s.hidden_size), torch.float32)
+        kernels.moe_down(hidden, found, self.w_down, pair_rows)
+        shared_rows = None
+        if s.shared_size:
+            shared_hidden = ctx.alloc((tokens, s.shared_size), dtype)
+            kernels.gate_up_silu(x, self.shared_gate_up, shared_hidden, ctx.alloc)
+            shared_rows = ctx.alloc((tokens, s.hidden_size), torch.float32)
+            kernels.linear(shared_hidden, self.shared_down, shared_rows, alloc=ctx.alloc)
+        kernels.moe_combine(residual, pair_rows, weights, shared_rows, gate)
+        ctx.residual_stats = None

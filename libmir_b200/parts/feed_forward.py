@@ -47,14 +47,17 @@ class SwiGlu(FeedForward):
 
 
 class GeluMlp(FeedForward):
-    """down(gelu_tanh(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit, in the
-    epilogue of the up projection where our own products run it, else on the product's rows, in place."""
+    """down(gelu(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit: the tanh form
+    in the epilogue of the up projection where our own products run it, else on the product's rows, in place; the
+    exact (erf) form always on the product's rows."""
 
     graph_safe = True
     takes_normed_residual = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
+        if spec.activation not in ("gelu_tanh", "gelu_erf"):
+            raise ValueError(f"unknown activation {spec.activation!r}")
         self.w_up = self.w_down = None
 
     def parameters(self):
@@ -71,5 +74,9 @@ class GeluMlp(FeedForward):
 
     def forward(self, ctx, x, residual):
         hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)   # (x may be a folded norm)
-        kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc)     # the activation in the product's epilogue
+        if self.spec.activation == "gelu_erf":
+            kernels.linear(x, self.w_up, hidden, alloc=ctx.alloc)
+            kernels.gelu_erf(hidden)
+        else:
+            kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc)     # the activation in the product's epilogue
         ctx.accumulate(hidden, self.w_down, residual)

@@ -101,15 +101,17 @@ def rotate_interleaved(x, positions, rot):
 def latent_attention(h, weights, prefix, mixer, eps):
     """Attention whose queries and keys / values come through low-rank latents; h [n, w]."""
     n = h.shape[0]
-    heads, dim, rot_dim, vdim, rank = (int(mixer[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank"))
+    heads, dim, vdim, rank = (int(mixer[k]) for k in ("heads", "dim", "vdim", "kv_rank"))
+    rot_dim = int(mixer.get("rot_dim", 0))
     w = lambda name: weights[prefix + name]
     positions = torch.arange(n)
     latent_q = unit_rms(h @ w("dq").T, eps) * w("dq.norm")
     q = (latent_q @ w("uq").T).reshape(n, heads, dim + rot_dim)
-    q_plain, q_rot = q[..., :dim], rotate_interleaved(q[..., dim:], positions, mixer["rot"])
     down = h @ w("dkv").T
     latent = unit_rms(down[:, :rank], eps) * w("dkv.norm")
-    k_rot = rotate_interleaved(down[:, rank:], positions, mixer["rot"])       # [n, rot_dim], one for all heads
+    q_plain, q_rot, k_rot = q[..., :dim], q[..., dim:], down[:, rank:]        # k_rot [n, rot_dim]: one for all heads
+    if rot_dim:
+        q_rot, k_rot = rotate_interleaved(q_rot, positions, mixer["rot"]), rotate_interleaved(k_rot, positions, mixer["rot"])
     k_plain = (latent @ w("uk").T).reshape(n, heads, dim)
     v = (latent @ w("uv").T).reshape(n, heads, vdim)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * float(mixer["scale"])

@@ -41,7 +41,7 @@ LIBRARIES = {
     "bf16": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
                     "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "attention_tc_decode.cu",
-                    "gemm_tc_stream.cu", "ops_bf16.cu", "executor.cu", "delta_rule.cu"],
+                    "gemm_tc_stream.cu", "ops_bf16.cu", "executor.cu", "delta_rule.cu", "latent_attention_mma.cu"],
         "headers": ["no_alloc.h", "tcgen05.cuh"],
         "link": ["-lcublasLt"],
         "defines": ["-DMIR_WITH_BF16"],

@@ -124,6 +124,10 @@ _SIGNATURES = {
                             c_void_p],
         "mir_gate_up_silu_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float,
                                   c_void_p, c_void_p, c_size_t, c_void_p],
+        "mir_latent_attention_takes": [c_int, c_int],
+        "mir_latent_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p],
         "mir_set_option": [ctypes.c_char_p, c_int],
         "mir_get_option": [ctypes.c_char_p],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -616,6 +620,56 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: 
     _check(lib, lib.mir_head_linear(_is_bf16(x), x.data_ptr(), x.stride(0), x.stride(1), weight.data_ptr(), out.data_ptr(),
                                     out.stride(0), out.stride(1), _ptr(gate), gate.stride(0) if gate is not None else 0,
                                     tokens, heads, in_dim, out_dim, _stream()))
+
+
+LATENT_TENSOR_CORES = True       # False: attention over cached latents always runs the reference kernel
+
+
+def latent_attention_takes(width: int, rank: int) -> bool:
+    """Whether the tensor-core kernel for attention over cached latents takes rows of `width` numbers whose first
+    `rank` are the value (bfloat16 only)."""
+    return bool(LATENT_TENSOR_CORES and library("bf16").mir_latent_attention_takes(width, rank))
+
+
+def latent_attention_plan(num_rows: int, max_pairs: int, max_context: int) -> tuple:
+    """(keys per partition, partitions) for a step of `num_rows` request rows, the largest of which brings max_pairs
+    (token, head) pairs, over at most max_context keys: the keys are split where the query rows alone would leave
+    most of the GPU idle (decoded tokens)."""
+    blocks = max(1, num_rows * (-(-max_pairs // 64)))
+    tiles = max(1, -(-max_context // 64))
+    sms = 148
+    partitions = 1 if blocks >= sms else max(1, min(tiles, (2 * sms) // blocks, 64))
+    per_partition = -(-tiles // partitions) * 64
+    return per_partition, -(-max_context // per_partition) if max_context > 0 else 1
+
+
+def latent_attention(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                     query_starts: torch.Tensor, context_lens: torch.Tensor, page_size: int, heads: int, width: int,
+                     rank: int, scale: float, max_pairs: int, partition_keys: int, partitions: int, alloc) -> None:
+    """out[t, h] = softmax over the cached rows of token t's request up to its own position, on tensor cores: q
+    [tokens, heads * width] bfloat16 folded queries, pages [cache rows, 1, width] of which the first `rank` numbers of
+    a row are its value, out [tokens, heads * rank].  Request row r brings the tokens query_starts[r] ..
+    query_starts[r + 1] and has context_lens[r] keys after the step.  With partitions > 1 the keys are walked in
+    shares of partition_keys and merged by a second kernel (scratch from `alloc`)."""
+    _cuda(q, out, pages, block_table, query_starts, context_lens)
+    tokens = q.shape[0]
+    rows = query_starts.numel() - 1
+    _require(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
+             and q.stride(1) == 1 and q.shape[1] == heads * width and out.is_contiguous()
+             and out.shape == (tokens, heads * rank) and pages.is_contiguous() and pages[0].numel() == width
+             and block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+             and block_table.shape[0] >= rows and query_starts.dtype == torch.int32 and context_lens.dtype == torch.int32
+             and context_lens.numel() >= rows, "latent_attention: shapes or dtypes do not fit")
+    partial_o = partial_ml = None
+    if partitions > 1:
+        partial_o = alloc((tokens * heads * partitions, rank), torch.float32)
+        partial_ml = alloc((tokens * heads * partitions, 2), torch.float32)
+    lib = library("bf16")
+    _check(lib, lib.mir_latent_attention_bf16(q.data_ptr(), q.stride(0), out.data_ptr(), pages.data_ptr(),
+                                              block_table.data_ptr(), block_table.shape[1], query_starts.data_ptr(),
+                                              context_lens.data_ptr(), rows, tokens, max_pairs, page_size, heads, width,
+                                              rank, scale, partition_keys, partitions, _ptr(partial_o), _ptr(partial_ml),
+                                              _stream()))
 
 
 # --------------------------------------------------------------------------- wkv

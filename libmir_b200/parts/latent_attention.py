@@ -126,6 +126,14 @@ class LatentAttention(Mixer):
         """Every packed row's folded query heads over its request's cached rows: one key head of kv_rank + rotary
         dims whose first kv_rank dims are the value."""
         s = self.spec
+        if self.env.dtype == torch.bfloat16 and kernels.latent_attention_takes(self.key_width, s.kv_rank):
+            # tensor cores: the (token, head) pairs of a request are the rows of one query matrix over its keys
+            max_pairs = max(1, ctx.max_portion) * s.heads
+            per_partition, partitions = kernels.latent_attention_plan(ctx.num_rows, max_pairs, ctx.max_context)
+            kernels.latent_attention(folded, out, cache.k_pages, group.block_table, ctx.query_starts, ctx.context_lens,
+                                     cache.page_size, s.heads, self.key_width, s.kv_rank, s.scale, max_pairs,
+                                     per_partition, partitions, ctx.alloc)
+            return
         kernels.paged_attention_generic(folded, out, cache.k_pages, None, group.block_table, ctx.row_of_token,
                                         ctx.positions, cache.page_size, s.heads, 1, self.key_width, s.scale, None,
                                         value_dim=s.kv_rank, values_in_keys=True)

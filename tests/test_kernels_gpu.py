@@ -304,10 +304,10 @@ def test_attention_sees_one_far_key_among_hundreds_and_the_windows_edge(dtype):
 
 def test_kernels_refuse_sizes_they_do_not_take():
     from libmir_b200 import KernelError, kernels
-    q = torch.zeros(1, 3 * 520, device="cuda")
-    with pytest.raises(KernelError, match="head_dim 520"):
-        kernels.paged_attention_generic(q, torch.zeros(1, 520, device="cuda"), torch.zeros(4, 1, 520, device="cuda"),
-                                        torch.zeros(4, 1, 520, device="cuda"),
+    q = torch.zeros(1, 3 * 648, device="cuda")
+    with pytest.raises(KernelError, match="head_dim 648"):
+        kernels.paged_attention_generic(q, torch.zeros(1, 648, device="cuda"), torch.zeros(4, 1, 648, device="cuda"),
+                                        torch.zeros(4, 1, 648, device="cuda"),
                                         torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
                                         torch.zeros(1, dtype=torch.int32, device="cuda"),
                                         torch.zeros(1, dtype=torch.int32, device="cuda"), 4, 1, 1, 520, 1.0, None)

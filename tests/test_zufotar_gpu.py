@@ -220,6 +220,63 @@ def test_attention_over_cached_latents_one_key_stands_out(dtype, tol, page_size,
         assert float(scores[1, target]) > 0.9
 
 
+@pytest.mark.parametrize("partitions", [1, 3])
+@pytest.mark.parametrize("heads,page_size,rank,rotary", [(3, 16, 24, 8), (16, 8, 64, 16), (5, 4, 128, 0), (16, 16, 512, 64),
+                                                         (70, 32, 40, 8)])
+def test_tensor_core_attention_over_cached_latents(heads, page_size, rank, rotary, partitions):
+    """The tile kernel on single tokens beside prompt portions that start in the middle of a request, with shuffled
+    pages and garbage in the rest of the pool: every (token, head) against a 64-bit softmax over the keys up to its
+    own position; one head of every query is made to look at one far key."""
+    from libmir_b200 import kernels
+    generator = torch.Generator().manual_seed(11)
+    width = rank + rotary
+    assert kernels.latent_attention_takes(width, rank)
+    # (tokens in the step, tokens cached before it) per request row; single tokens first, as the engine packs them
+    rows = [(1, 0), (1, 63), (1, 64), (1, 700), (2, 0), (65, 3), (130, 200), (17, 47)]
+    contexts = [n + before for n, before in rows]
+    pages_per = [-(-c // page_size) for c in contexts]
+    order = torch.randperm(sum(pages_per) + 2, generator=generator).tolist()
+    table = torch.full((len(rows), max(pages_per)), -1, dtype=torch.int32)
+    cache = torch.randn((sum(pages_per) + 2) * page_size, 1, width, generator=generator) * 30.0
+    keys, cursor = [], 0
+    for row, context in enumerate(contexts):
+        k = (torch.randn(context, width, generator=generator) * 0.4).to(torch.bfloat16).float()
+        keys.append(k)
+        for block in range(pages_per[row]):
+            page = order[cursor]
+            cursor += 1
+            table[row, block] = page
+            chunk = k[block * page_size:(block + 1) * page_size]
+            cache[page * page_size:page * page_size + chunk.shape[0], 0] = chunk
+    tokens = sum(n for n, _ in rows)
+    q = torch.randn(tokens, heads, width, generator=generator) * 0.3
+    starts, at = [0], 0
+    for row, (n, before) in enumerate(rows):
+        for i in range(n):
+            target = (before + i) // 3                                      # a key well behind the query
+            q[at + i, (at + i) % heads] += keys[row][target] * (40.0 / max(1.0, float(keys[row][target].norm()) ** 2) * 8.0)
+        at += n
+        starts.append(at)
+    q = q.to(torch.bfloat16)
+    out = torch.empty(tokens, heads * rank, dtype=torch.bfloat16, device=device())
+    alloc = lambda shape, kind: torch.empty(shape, dtype=kind, device=device())
+    longest = max(contexts)
+    per_partition = -(-(-(-longest // 64)) // partitions) * 64
+    kernels.latent_attention(on_device(q).view(tokens, heads * width), out, on_device(cache.to(torch.bfloat16)), on_device(table),
+                             on_device(torch.tensor(starts, dtype=torch.int32)), on_device(torch.tensor(contexts, dtype=torch.int32)),
+                             page_size, heads, width, rank, 0.5, max(n for n, _ in rows) * heads, per_partition,
+                             -(-longest // per_partition), alloc)
+    got = out.float().cpu().view(tokens, heads, rank)
+    at = 0
+    for row, (n, before) in enumerate(rows):
+        k = keys[row].double()
+        for i in range(n):
+            visible = k[:before + i + 1]
+            weights = torch.softmax((q[at + i].double() @ visible.T) * 0.5, dim=-1)
+            close(got[at + i], weights @ visible[:, :rank], 2e-2, f"row {row}, token {i} of {n} after {before}")
+        at += n
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_blends_with_the_token_before_carry_over_portions(dtype):
     """wkv_mix: the token before a portion's first token is the request's state (zeros at its start); slots of other

@@ -3,9 +3,11 @@
 //   moe_route     per token: 32-bit router logits, sigmoid scores, choice among the experts of the best groups by
 //                 score + correction, weights = chosen scores / their sum * scale; and the shared expert's gate
 //   moe_sort      the pairs ordered by expert (a stable counting sort inside one CTA), each expert's range, and the
-//                 list of tiles of kExpertTile pairs of one expert that the grouped products walk over
+//                 list of tiles (8 or 64 pairs of one expert) that the grouped products walk over
 //   moe_grouped   products on the sorted pairs with each pair's own expert's weights: hidden = silu(Wg x) * (Wu x)
-//                 from the tokens' rows, and the down projection of the hidden rows into one 32-bit row per pair
+//                 from the tokens' rows, and the down projection of the hidden rows into one 32-bit row per pair;
+//                 32-bit multiply-adds on tiles of 8 pairs (any type and size), or bf16 tensor cores (mma.sync
+//                 m16n8k16) on tiles of 64 pairs x 64 outputs with the weights streamed through a cp.async ring
 //   moe_combine   residual[t] += sum over slots of weight * the pair's row (+ gate * the shared expert's row)
 // Everything the host needs to launch them is known before the step: no count is read back.
 #include <cfloat>
@@ -95,8 +97,9 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long long ld, const fl
 // One CTA of 1024 threads.  order[i] = the i-th pair when the pairs are sorted by expert (pairs of one expert stay in
 // their own order); offsets[e] .. offsets[e + 1] is expert e's range in it; tiles[2 n], tiles[2 n + 1] = expert and
 // first sorted pair of the n-th tile, tile_count[0] = how many there are.
-__global__ void moe_sort_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ order,
-                                int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ tile_count) {
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int pairs, int experts, int tile_pairs,
+                                int* __restrict__ order, int* __restrict__ offsets, int* __restrict__ tiles,
+                                int* __restrict__ tile_count) {
   __shared__ int count[kMaxExperts + 1];
   __shared__ int first[kMaxExperts + 1];
   __shared__ int first_tile[kMaxExperts + 1];
@@ -116,7 +119,7 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, int pairs, int expe
       first_tile[e] = tile;
       offsets[e] = at;
       at += count[e];
-      tile += (count[e] + kExpertTile - 1) / kExpertTile;
+      tile += (count[e] + tile_pairs - 1) / tile_pairs;
     }
     first[experts] = at;
     offsets[experts] = at;
@@ -131,10 +134,10 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, int pairs, int expe
       if (mine) order[at + __popc(ballot & ((1u << lane) - 1u))] = p;
       at += __popc(ballot);
     }
-    const int n = (count[e] + kExpertTile - 1) / kExpertTile;
+    const int n = (count[e] + tile_pairs - 1) / tile_pairs;
     for (int t = lane; t < n; t += 32) {
       tiles[2 * (first_tile[e] + t)] = e;
-      tiles[2 * (first_tile[e] + t) + 1] = first[e] + t * kExpertTile;
+      tiles[2 * (first_tile[e] + t) + 1] = first[e] + t * tile_pairs;
     }
   }
 }
@@ -240,6 +243,136 @@ moe_grouped_kernel(const T* __restrict__ x, long long ldx, const int* __restrict
   }
 }
 
+// ---- the grouped products on tensor cores (bf16) -------------------------------------------------------------------
+constexpr int kMmaTile = 64;          // pairs of one expert per CTA
+constexpr int kMmaColumns = 64;       // outputs per CTA
+constexpr int kMmaStep = 32;          // inputs per stage
+constexpr int kMmaLd = kMmaStep + 8;  // row stride in shared memory: 80 bytes, so that ldmatrix meets no bank twice
+
+__device__ __forceinline__ void mma_ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_ldmatrix_x2(unsigned (&r)[2], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma_copy16(void* dst, const void* src) {
+  const unsigned target = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(src) : "memory");
+}
+
+// 128 threads; grid (tile slots, ceil(N / 64)).  A CTA takes up to 64 sorted pairs of one expert and 64 outputs
+// (GATED: 64 gate and the 64 up rows beside them); each of its 4 warps 16 pairs.  K is a multiple of 8.  Rows and
+// results as in moe_grouped_kernel.
+template <bool GATED, typename TO>
+__global__ void __launch_bounds__(128)
+moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ gather, int gather_div,
+                       const __nv_bfloat16* __restrict__ w_a, const __nv_bfloat16* __restrict__ w_b, TO* __restrict__ out,
+                       long long ldo, const int* __restrict__ scatter, const int* __restrict__ tiles,
+                       const int* __restrict__ tile_count, const int* __restrict__ offsets, int K, int N) {
+  constexpr int WEIGHT_ROWS = GATED ? 2 * kMmaColumns : kMmaColumns;
+  __shared__ __align__(16) __nv_bfloat16 a_s[2][kMmaTile][kMmaLd];
+  __shared__ __align__(16) __nv_bfloat16 b_s[2][WEIGHT_ROWS][kMmaLd];
+  __shared__ int source[kMmaTile];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  if ((int)blockIdx.x >= tile_count[0]) return;
+  const int thread = threadIdx.x, lane = thread & 31, warp = thread >> 5;
+  const int expert = tiles[2 * blockIdx.x], start = tiles[2 * blockIdx.x + 1];
+  const int count = min(kMmaTile, offsets[expert + 1] - start);
+  const int first_output = blockIdx.y * kMmaColumns;
+  if (thread < kMmaTile)
+    source[thread] = thread < count ? (gather != nullptr ? gather[start + thread] / gather_div : start + thread) : -1;
+  __syncthreads();
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  auto stage_in = [&](int stage, int k0) {
+    for (int index = thread; index < kMmaTile * 4; index += 128) {
+      const int r = index >> 2, c = (index & 3) * 8;
+      if (source[r] >= 0 && k0 + c < K) mma_copy16(&a_s[stage][r][c], x + (size_t)source[r] * ldx + k0 + c);
+      else *reinterpret_cast<uint4*>(&a_s[stage][r][c]) = zero;
+    }
+    for (int index = thread; index < WEIGHT_ROWS * 4; index += 128) {
+      const int r = index >> 2, c = (index & 3) * 8;
+      const int o = first_output + (r % kMmaColumns);
+      const __nv_bfloat16* w = (GATED && r >= kMmaColumns) ? w_b : w_a;
+      if (o < N && k0 + c < K) mma_copy16(&b_s[stage][r][c], w + ((size_t)expert * N + o) * K + k0 + c);
+      else *reinterpret_cast<uint4*>(&b_s[stage][r][c]) = zero;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc_a[8][4], acc_b[GATED ? 8 : 1][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      acc_a[nt][e] = 0.0f;
+      if (GATED) acc_b[nt][e] = 0.0f;
+    }
+  stage_in(0, 0);
+  int stage = 0;
+  for (int k0 = 0; k0 < K; k0 += kMmaStep, stage ^= 1) {
+    if (k0 + kMmaStep < K) {
+      stage_in(stage ^ 1, k0 + kMmaStep);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < kMmaStep; ks += 16) {
+      unsigned a[4];
+      mma_ldmatrix_x4(a, &a_s[stage][warp * 16 + (lane & 15)][ks + (lane >> 4) * 8]);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        unsigned b[2];
+        mma_ldmatrix_x2(b, &b_s[stage][nt * 8 + (lane & 7)][ks + ((lane >> 3) & 1) * 8]);
+        mma_bf16(acc_a[nt], a, b);
+        if (GATED) {
+          mma_ldmatrix_x2(b, &b_s[stage][kMmaColumns + nt * 8 + (lane & 7)][ks + ((lane >> 3) & 1) * 8]);
+          mma_bf16(acc_b[nt], a, b);
+        }
+      }
+    }
+    __syncthreads();                                             // the stage is free for the step after next
+  }
+  const int g = lane >> 2, c2 = (lane & 3) * 2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = warp * 16 + g + half * 8;
+    if (r >= count) continue;
+    const int to = scatter != nullptr ? scatter[start + r] : start + r;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int o = first_output + nt * 8 + c2 + e;
+        if (o >= N) continue;
+        const float a = acc_a[nt][half * 2 + e];
+        const float value = GATED ? a / (1.0f + expf(-a)) * acc_b[nt][half * 2 + e] : a;
+        out[(size_t)to * ldo + o] = from_float<TO>(value);
+      }
+    }
+  }
+}
+
+template <bool GATED, typename TO>
+int launch_grouped_mma(cudaStream_t stream, const void* x, long long ldx, const int* gather, int gather_div,
+                       const void* w_a, const void* w_b, void* out, long long ldo, const int* scatter, const int* tiles,
+                       const int* tile_count, const int* offsets, int pairs, int experts, int K, int N) {
+  const int slots = pairs / kMmaTile + experts;
+  const dim3 grid(slots, (N + kMmaColumns - 1) / kMmaColumns);
+  return mir_launch(GATED ? "moe_grouped_mma_gate_up" : "moe_grouped_mma_down", moe_grouped_mma_kernel<GATED, TO>, grid,
+                    dim3(128), 0, stream, 0, (const __nv_bfloat16*)x, ldx, gather, gather_div, (const __nv_bfloat16*)w_a,
+                    (const __nv_bfloat16*)w_b, (TO*)out, ldo, scatter, tiles, tile_count, offsets, K, N);
+}
+
 // One CTA per token: residual[t] += sum_s weights[t, s] * pair_rows[t * top + s] (+ shared_gate[t] * shared_rows[t], or
 // + shared_rows[t] without a gate), slots in their own order.
 __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ pair_rows,
@@ -292,26 +425,34 @@ MIR_EXPORT int mir_moe_route(int bf16, const void* h, long long ld, const float*
                     router, correction, shared_gate_w, ids, weights, shared_gate, width, experts, top, groups, keep, scale);
 }
 
-// How many ints `tiles` must hold for `pairs` pairs over `experts` experts.
-MIR_EXPORT int mir_moe_tile_slots(int pairs, int experts) { return pairs / kExpertTile + experts; }
+// How many tiles of tile_pairs pairs there can be at most for `pairs` pairs over `experts` experts (`tiles` holds two
+// ints for each).
+MIR_EXPORT int mir_moe_tile_slots(int pairs, int experts, int tile_pairs) { return pairs / tile_pairs + experts; }
 
-MIR_EXPORT int mir_moe_sort(const int* ids, int pairs, int experts, int* order, int* offsets, int* tiles, int* tile_count,
-                            cudaStream_t stream) {
+// tile_pairs: 8 for the 32-bit grouped products, 64 for the tensor-core ones.
+MIR_EXPORT int mir_moe_sort(const int* ids, int pairs, int experts, int tile_pairs, int* order, int* offsets, int* tiles,
+                            int* tile_count, cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
-  if (pairs < 0 || experts <= 0 || experts > kMaxExperts) {
-    mir_set_error("moe_sort: bad sizes (pairs %d, experts %d)", pairs, experts);
+  if (pairs < 0 || experts <= 0 || experts > kMaxExperts || (tile_pairs != kExpertTile && tile_pairs != kMmaTile)) {
+    mir_set_error("moe_sort: bad sizes (pairs %d, experts %d, tiles of %d)", pairs, experts, tile_pairs);
     return MIR_BAD_ARGUMENT;
   }
-  return mir_launch("moe_sort", moe_sort_kernel, dim3(1), dim3(1024), 0, stream, 0, ids, pairs, experts, order, offsets,
-                    tiles, tile_count);
+  return mir_launch("moe_sort", moe_sort_kernel, dim3(1), dim3(1024), 0, stream, 0, ids, pairs, experts, tile_pairs, order,
+                    offsets, tiles, tile_count);
 }
 
 // hidden[i] = silu(w_gate[e] x) * (w_up[e] x) for the i-th sorted pair, x the row of its token (order[i] / top) of h.
 // w_gate, w_up [experts, inter, width]; hidden [pairs, inter] in the activations' type.
 MIR_EXPORT int mir_moe_gate_up(int bf16, const void* h, long long ld, const int* order, int top, const void* w_gate,
                                const void* w_up, void* hidden, const int* tiles, const int* tile_count,
-                               const int* offsets, int pairs, int experts, int width, int inter, cudaStream_t stream) {
+                               const int* offsets, int pairs, int experts, int width, int inter, int tile_pairs,
+                               cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
+  if (tile_pairs == kMmaTile) {
+    if (!bf16 || width % 8 || ld % 8) { mir_set_error("moe_gate_up: tiles of 64 pairs need bfloat16 rows of 16-byte pieces"); return MIR_BAD_ARGUMENT; }
+    return launch_grouped_mma<true, __nv_bfloat16>(stream, h, ld, order, top, w_gate, w_up, hidden, inter, nullptr, tiles,
+                                                   tile_count, offsets, pairs, experts, width, inter);
+  }
   if (bf16)
     return launch_grouped<__nv_bfloat16, __nv_bfloat16, true>(stream, h, ld, order, top, w_gate, w_up, hidden, inter,
                                                               nullptr, tiles, tile_count, offsets, pairs, experts, width,
@@ -323,8 +464,13 @@ MIR_EXPORT int mir_moe_gate_up(int bf16, const void* h, long long ld, const int*
 // pair_rows[order[i]] = w_down[e] hidden[i]: one 32-bit row [width] per pair, at the pair's own index.
 MIR_EXPORT int mir_moe_down(int bf16, const void* hidden, const int* order, const void* w_down, float* pair_rows,
                             const int* tiles, const int* tile_count, const int* offsets, int pairs, int experts,
-                            int width, int inter, cudaStream_t stream) {
+                            int width, int inter, int tile_pairs, cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
+  if (tile_pairs == kMmaTile) {
+    if (!bf16 || inter % 8) { mir_set_error("moe_down: tiles of 64 pairs need bfloat16 rows of 16-byte pieces"); return MIR_BAD_ARGUMENT; }
+    return launch_grouped_mma<false, float>(stream, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows, width, order,
+                                            tiles, tile_count, offsets, pairs, experts, inter, width);
+  }
   if (bf16)
     return launch_grouped<__nv_bfloat16, float, false>(stream, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows,
                                                        width, order, tiles, tile_count, offsets, pairs, experts, inter,

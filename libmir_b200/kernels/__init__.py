@@ -64,12 +64,12 @@ _SIGNATURES = {
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_route": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                           c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
-        "mir_moe_tile_slots": [c_int, c_int],
-        "mir_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "mir_moe_tile_slots": [c_int, c_int, c_int],
+        "mir_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "mir_moe_gate_up": [c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_down": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                         c_int, c_void_p],
+                         c_int, c_int, c_void_p],
         "mir_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
@@ -750,24 +750,34 @@ class ExpertOrder:
     """The pairs (token, chosen expert) of a step ordered by expert, on the device: order [pairs] (sorted place ->
     pair), offsets [experts + 1], tiles [2 * slots] and tile_count [1] for the grouped products."""
 
-    def __init__(self, alloc, pairs: int, experts: int):
+    def __init__(self, alloc, pairs: int, experts: int, tile_pairs: int = 8):
         lib = library("core")
-        slots = int(lib.mir_moe_tile_slots(pairs, experts))
-        self.pairs, self.experts = pairs, experts
+        slots = int(lib.mir_moe_tile_slots(pairs, experts, tile_pairs))
+        self.pairs, self.experts, self.tile_pairs = pairs, experts, tile_pairs
         self.order = alloc((pairs,), torch.int32)
         self.offsets = alloc((experts + 1,), torch.int32)
         self.tiles = alloc((2 * slots,), torch.int32)
         self.tile_count = alloc((1,), torch.int32)
 
 
-def moe_sort(ids: torch.Tensor, experts: int, alloc) -> ExpertOrder:
-    """Order the pairs of ids [tokens, top] by expert (a pair's place among its expert's pairs follows its index)."""
+EXPERT_TENSOR_CORES = True       # False: the grouped products of routed experts always run as 32-bit multiply-adds
+
+
+def expert_tile_pairs(dtype: torch.dtype, width: int, inter: int) -> int:
+    """The tile the grouped products of routed experts work on: 64 pairs on tensor cores (bfloat16 rows of 16-byte
+    pieces), else 8 pairs with 32-bit multiply-adds."""
+    return 64 if (EXPERT_TENSOR_CORES and dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0) else 8
+
+
+def moe_sort(ids: torch.Tensor, experts: int, alloc, tile_pairs: int = 8) -> ExpertOrder:
+    """Order the pairs of ids [tokens, top] by expert (a pair's place among its expert's pairs follows its index) and
+    cut each expert's run into tiles of tile_pairs (8 or 64) pairs."""
     _cuda(ids)
     _require(ids.dtype == torch.int32 and ids.is_contiguous(), "moe_sort: contiguous int32 ids are needed")
-    found = ExpertOrder(alloc, ids.numel(), experts)
+    found = ExpertOrder(alloc, ids.numel(), experts, tile_pairs)
     lib = library("core")
-    _check(lib, lib.mir_moe_sort(ids.data_ptr(), ids.numel(), experts, found.order.data_ptr(), found.offsets.data_ptr(),
-                                 found.tiles.data_ptr(), found.tile_count.data_ptr(), _stream()))
+    _check(lib, lib.mir_moe_sort(ids.data_ptr(), ids.numel(), experts, tile_pairs, found.order.data_ptr(),
+                                 found.offsets.data_ptr(), found.tiles.data_ptr(), found.tile_count.data_ptr(), _stream()))
     return found
 
 
@@ -786,7 +796,7 @@ def moe_gate_up(h: torch.Tensor, found: ExpertOrder, top: int, w_gate: torch.Ten
     _check(lib, lib.mir_moe_gate_up(_is_bf16(h), h.data_ptr(), h.stride(0), found.order.data_ptr(), top,
                                     w_gate.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), found.tiles.data_ptr(),
                                     found.tile_count.data_ptr(), found.offsets.data_ptr(), found.pairs, experts, width,
-                                    inter, _stream()))
+                                    inter, found.tile_pairs, _stream()))
 
 
 def moe_down(hidden: torch.Tensor, found: ExpertOrder, w_down: torch.Tensor, pair_rows: torch.Tensor) -> None:
@@ -800,7 +810,7 @@ def moe_down(hidden: torch.Tensor, found: ExpertOrder, w_down: torch.Tensor, pai
     lib = library("core")
     _check(lib, lib.mir_moe_down(_is_bf16(hidden), hidden.data_ptr(), found.order.data_ptr(), w_down.data_ptr(),
                                  pair_rows.data_ptr(), found.tiles.data_ptr(), found.tile_count.data_ptr(),
-                                 found.offsets.data_ptr(), found.pairs, experts, width, inter, _stream()))
+                                 found.offsets.data_ptr(), found.pairs, experts, width, inter, found.tile_pairs, _stream()))
 
 
 def moe_combine(residual: torch.Tensor, pair_rows: torch.Tensor, weights: torch.Tensor,

@@ -9,8 +9,9 @@ With h the feed-forward's input, E experts of which each token uses `top`:
     out = sum over chosen of weight * expert(h)    expert(h) = W_down (silu(W_gate h) * (W_up h))
         + sigmoid(w_sg . h) * shared(h)            one number per token gates the shared expert, if there is one
 Everything runs on the device without a count ever being read back (csrc/moe.cu): the (token, expert) pairs are
-ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights, and one kernel
-adds the weighted rows, and the shared expert's, into the 32-bit residual.
+ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights (on tensor
+cores in bfloat16, as 32-bit multiply-adds in float32), and one kernel adds the weighted rows, and the shared
+expert's, into the 32-bit residual.
 """
 
 from __future__ import annotations
@@ -79,7 +80,7 @@ class RoutedExperts(FeedForward):
         gate = ctx.alloc((tokens,), torch.float32) if self.shared_gate is not None else None
         kernels.moe_route(x, self.router, self.correction, self.shared_gate, ids, weights, gate, s.top, s.groups,
                           s.keep_groups, s.scale)
-        found = kernels.moe_sort(ids, s.experts, ctx.alloc)
+        found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size))
         hidden = ctx.alloc((tokens * s.top, s.expert_size), dtype)
         kernels.moe_gate_up(x, found, s.top, self.w_gate, self.w_up, hidden)
         pair_rows = ctx.alloc((tokens * s.top, s.hidden_size), torch.float32)

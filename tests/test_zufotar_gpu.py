@@ -411,10 +411,11 @@ def test_router_against_the_plain_one(dtype, experts, top, groups, keep):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("tokens,experts,top,width,inter", [(1, 4, 2, 32, 16), (7, 3, 3, 52, 20), (100, 16, 4, 64, 40),
-                                                            (33, 5, 1, 600, 24), (9, 40, 2, 24, 7)])
+                                                            (33, 5, 1, 600, 24), (9, 40, 2, 24, 7), (300, 3, 2, 72, 136)])
 def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, experts, top, width, inter):
-    """Sorting by expert, the two grouped products and the weighted sum: experts without any token, experts with
-    more pairs than a tile, a shared expert with and without gate."""
+    """Sorting by expert, the two grouped products (32-bit multiply-adds on tiles of 8 pairs, or tensor cores on
+    tiles of 64 where the sizes allow) and the weighted sum: experts without any token, experts with more pairs than
+    a tile, a shared expert with and without gate."""
     from libmir_b200 import kernels
     generator = torch.Generator().manual_seed(10)
     h = torch.randn(tokens, width, generator=generator).to(dtype)
@@ -425,7 +426,9 @@ def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, exp
         ids[ids == 1] = 0                                                    # expert 1 gets no token
     weights = torch.rand(tokens, top, generator=generator)
     alloc = lambda shape, kind: torch.empty(shape, dtype=kind, device=device())
-    found = kernels.moe_sort(on_device(ids), experts, alloc)
+    tile = kernels.expert_tile_pairs(dtype, width, inter)
+    assert tile == (64 if dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0 else 8)
+    found = kernels.moe_sort(on_device(ids), experts, alloc, tile)
     order, offsets = found.order.cpu().tolist(), found.offsets.cpu().tolist()
     flat = ids.reshape(-1).tolist()
     assert sorted(order) == list(range(tokens * top)) and offsets[0] == 0 and offsets[-1] == tokens * top
@@ -437,7 +440,7 @@ def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, exp
     covered = []
     for n in range(count):
         expert, start = tiles[2 * n], tiles[2 * n + 1]
-        covered += list(range(start, min(start + 8, offsets[expert + 1])))
+        covered += list(range(start, min(start + tile, offsets[expert + 1])))
         assert offsets[expert] <= start < offsets[expert + 1]
     assert sorted(covered) == list(range(tokens * top))
     hidden = torch.empty(tokens * top, inter, dtype=dtype, device=device())

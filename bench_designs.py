@@ -1,6 +1,7 @@
-"""`bench.py --design doderax`: prefill and decode throughput of the Doderax design at layer sizes that resemble a
-real model's (random weights), beside the dense SwiGLU decoder of equal width, depth and parameter count, and every
-kernel the design adds alone, with the fraction of its roofline, beside the like kernel of the dense decoder.
+"""`bench.py --design doderax | zufotar`: prefill and decode throughput of a design at layer sizes that resemble a
+real model's (random weights), beside the dense SwiGLU decoder of equal width, depth and parameter count (and, for
+Zufotar, beside Doderax, the closest model of the framework: recurrent mixers and attention in parallel layers), and
+every kernel the design adds alone, with the fraction of its roofline, beside the like kernel of the closest model.
 
 A kernel alone is launched 24 times inside one CUDA graph on rotating copies of its operands (together more than the
 L2 holds); the graph is replayed five times and the median time per launch is taken from CUDA events.
@@ -19,6 +20,207 @@ DESIGN_SIZES = {
     "w2048": dict(width=2048, ff=8192, layers=12, heads=16, kv_heads=4, dim=128, window=1024, keep_first=4, vocab=65536),
     "w4096": dict(width=4096, ff=14336, layers=8, heads=32, kv_heads=8, dim=128, window=2048, keep_first=4, vocab=65536),
 }
+
+
+# Zufotar: latent attention and wkv layers in turn; the first feed-forward dense, the others routed experts; layers
+# 2 and 3 run twice.  `runs` is the number of layer runs of a step, the depth of the models it is put beside.
+ZUFOTAR_SIZES = {
+    "w2048": dict(width=2048, layers=8, runs=10, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512,
+                  wkv_heads=32, wkv_dim=64, decay_rank=64, ff=8192, experts=64, top=6, expert_ff=1024, groups=(8, 4),
+                  shared_ff=2048, vocab=65536, kv_heads=4, window=1024, keep_first=4),
+    "w4096": dict(width=4096, layers=6, runs=8, heads=32, dim=128, rot=64, vdim=128, q_rank=1536, kv_rank=512,
+                  wkv_heads=64, wkv_dim=64, decay_rank=64, ff=14336, experts=64, top=6, expert_ff=2048, groups=(8, 4),
+                  shared_ff=4096, vocab=65536, kv_heads=8, window=2048, keep_first=4),
+}
+
+
+def zufotar_config(s: dict) -> dict:
+    latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot"], "vdim": s["vdim"], "q_rank": s["q_rank"],
+              "kv_rank": s["kv_rank"], "scale": (s["dim"] + s["rot"]) ** -0.5,
+              "rot": {"dims": s["rot"], "base": 1000000.0,
+                      "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    wkv = {"heads": s["wkv_heads"], "dim": s["wkv_dim"], "decay_rank": s["decay_rank"]}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]},
+           "router": {"experts": s["experts"], "top": s["top"], "scale": 2.5,
+                      "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
+    layers = []
+    for index in range(s["layers"]):
+        mixer = {"type": "latent_attention", "mixer": latent} if index % 2 == 0 else {"type": "wkv", "mixer": wkv}
+        layers.append(dict(mixer, mlp={"kind": "dense", "ff": s["ff"]} if index == 0 else moe))
+    return {"architecture": "Zufotar", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_softcap": 30.0, "loop": {"start": 2, "stop": 4, "times": 2},
+            "layers": layers}
+
+
+def zufotar_kernel_table(s, tools) -> dict:
+    """Every kernel the design adds, alone, at the sizes of a 2,048-token prompt and of a step of 8 decoded tokens:
+    [microseconds, fraction of its roofline], beside the like kernel of the closest model."""
+    import torch
+    from libmir_b200 import kernels
+    timed, copies, rand, device, hbm, flops_peak = (tools[k] for k in ("timed", "copies", "rand", "device", "hbm", "flops_peak"))
+    bf16, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    width, heads, dim, rot, vdim, rank = s["width"], s["heads"], s["dim"], s["rot"], s["vdim"], s["kv_rank"]
+    key_width = rank + rot
+    table = {}
+    alloc = lambda shape, kind: torch.empty(shape, dtype=kind, device=device)
+    for label, rows, portion in ((f"prefill_{PROMPT}", 1, PROMPT), (f"decode_b{BATCH}", BATCH, 1)):
+        tokens = rows * portion
+        starts = torch.arange(0, tokens + 1, portion, dtype=i32, device=device)
+        row_of = torch.arange(tokens, dtype=i32, device=device) // portion
+        slots = torch.arange(rows, dtype=i32, device=device)
+        context = PROMPT if portion > 1 else PROMPT + 1
+        positions = (torch.arange(tokens, dtype=i32, device=device) % portion) + (context - portion)
+        prompt = portion > 1
+        # ---- attention over cached latents, beside the dense decoder's attention over all keys
+        pages_per_row = -(-(context + PAGE) // PAGE)
+        cache_rows = rows * pages_per_row * PAGE
+        caches = [rand(cache_rows, 1, key_width, scale=0.5)
+                  for _ in range(max(2, min(24, -(-(300 << 20) // (cache_rows * key_width * 2)))))]
+        block_table = torch.arange(rows * pages_per_row, dtype=i32, device=device).view(rows, pages_per_row).contiguous()
+        contexts = torch.full((rows,), context, dtype=i32, device=device)
+        folded = rand(tokens, heads * key_width, scale=0.3)
+        attended = torch.empty(tokens, heads * rank, device=device, dtype=bf16)
+        per_partition, partitions = kernels.latent_attention_plan(rows, portion * heads, context)
+        scale = (dim + rot) ** -0.5
+        calls = [lambda c=c: kernels.latent_attention(folded, attended, c, block_table, starts, contexts, PAGE, heads,
+                                                      key_width, rank, scale, portion * heads, per_partition, partitions,
+                                                      alloc) for c in caches]
+        if prompt:
+            flops = 2.0 * (PROMPT * (PROMPT + 1) / 2) * heads * (key_width + rank)
+            table[f"{label}_latent_attention"] = timed(calls, flops, flops_peak)
+        else:
+            table[f"{label}_latent_attention"] = timed(calls, rows * context * key_width * 2, hbm)
+        kv_heads = s["kv_heads"]
+        k_cache = [rand(cache_rows, kv_heads, dim, scale=0.5) for _ in range(max(2, min(24, -(-(300 << 20) // (cache_rows * kv_heads * dim * 4)))))]
+        v_cache = [rand(cache_rows, kv_heads, dim, scale=0.5) for _ in k_cache]
+        qkv = rand(tokens, (heads + 2 * kv_heads) * dim, scale=0.3)
+        mixed = torch.empty(tokens, heads * dim, device=device, dtype=bf16)
+        if prompt:
+            calls = [lambda k=k, v=v: kernels.prefill_attention(qkv, mixed, k, v, block_table, starts, contexts, PAGE, heads,
+                                                                 kv_heads, dim, dim ** -0.5, None) for k, v in zip(k_cache, v_cache)]
+            table[f"{label}_dense_attention_full"] = timed(calls, 4.0 * (PROMPT * (PROMPT + 1) / 2) * dim * heads, flops_peak)
+        else:
+            q_positions = torch.full((tokens,), context - 1, dtype=i32, device=device)
+            partition, count, floats = kernels.decode_attention_plan(rows, heads, kv_heads, dim, PAGE, context)
+            scratch = torch.empty(max(floats, 1), device=device, dtype=f32)
+            calls = [lambda k=k, v=v: kernels.decode_attention(qkv, mixed, k, v, block_table, q_positions, PAGE, heads, kv_heads,
+                                                                dim, dim ** -0.5, None, partition, count,
+                                                                scratch if floats else None) for k, v in zip(k_cache, v_cache)]
+            table[f"{label}_dense_attention_full"] = timed(calls, rows * context * kv_heads * dim * 2 * 2, hbm)
+        # ---- the products per head around it, the latents' norms and the rotation
+        q = rand(tokens, heads, dim + rot, scale=0.3)
+        w_uk = rand(heads, dim, rank, scale=0.05)
+        folded3 = folded.view(tokens, heads, key_width)
+        calls = [lambda: kernels.head_linear(q[:, :, :dim], w_uk, folded3[:, :, :rank])]
+        work = 2.0 * tokens * heads * dim * rank
+        table[f"{label}_head_linear_keys_into_queries"] = timed(calls, work, flops_peak) if prompt else \
+            timed(calls, heads * dim * rank * 2, hbm)
+        w_uv = rand(heads, rank, vdim, scale=0.05)
+        gate = rand(tokens, heads * vdim)
+        values = torch.empty(tokens, heads, vdim, device=device, dtype=bf16)
+        calls = [lambda: kernels.head_linear(attended.view(tokens, heads, rank), w_uv, values, gate)]
+        table[f"{label}_head_linear_values_gated"] = timed(calls, 2.0 * tokens * heads * rank * vdim, flops_peak) if prompt else \
+            timed(calls, heads * rank * vdim * 2, hbm)
+        packed = rand(tokens, s["q_rank"] + key_width + 8)
+        inv_freq = torch.rand(rot // 2, device=device, dtype=f32)
+        latent_q = torch.empty(tokens, s["q_rank"], device=device, dtype=bf16)
+        slot_map = torch.arange(tokens, dtype=i32, device=device)
+        ones_q, ones_kv = torch.ones(s["q_rank"], device=device), torch.ones(rank, device=device)
+        calls = [lambda c=c: kernels.latent_prepare(packed, 0, s["q_rank"], s["q_rank"], rank, rot, ones_q, ones_kv, 1e-6,
+                                                    positions, slot_map, inv_freq, 1.1, True, latent_q, c) for c in caches]
+        table[f"{label}_latent_prepare"] = timed(calls, tokens * (s["q_rank"] + key_width) * 4, hbm)
+        calls = [lambda: kernels.rope_rows(q[:, :, dim:], folded3[:, :, rank:], positions, inv_freq, 1.1, True)]
+        table[f"{label}_rope_rows"] = timed(calls, tokens * heads * rot * 4, hbm)
+        # ---- wkv, beside the gated delta rule with one decay per key channel at the same heads
+        wh, wd = s["wkv_heads"], s["wkv_dim"]
+        wwidth = wh * wd
+        packs = copies(lambda: (torch.zeros(rows, wh, wd, wd, device=device, dtype=f32), rand(3, tokens, wwidth, scale=0.3),
+                                rand(tokens, wwidth, dtype=f32)), rows * wh * wd * wd * 4)
+        bias, bonus = rand(wwidth, dtype=f32), rand(wwidth, dtype=f32, scale=0.3)
+        out = torch.empty(tokens, wwidth, device=device, dtype=f32)
+        calls = [lambda p=p: kernels.wkv_scan(p[1][0], p[1][1], p[1][2], p[2], bias, bonus, p[0], starts, slots, positions, out,
+                                              wh, wd) for p in packs]
+        state_bytes = rows * wh * wd * wd * 4 * 2 + tokens * wwidth * (3 * 2 + 4 + 4)
+        note = ["of the bf16 tensor peak; the kernel is 32-bit FMA, one token after the other"]
+        table[f"{label}_wkv_scan"] = timed(calls, 4.0 * tokens * wh * wd * wd, flops_peak) + note if prompt else timed(calls, state_bytes, hbm)
+        packs = copies(lambda: (torch.zeros(rows, wh, wd, wd, device=device, dtype=f32), rand(tokens, 3 * wwidth, dtype=f32, scale=0.1)),
+                       rows * wh * wd * wd * 4)
+        beta = torch.rand(tokens, wh, device=device, dtype=f32)
+        decay = torch.rand(tokens, wwidth, device=device, dtype=f32) * 0.5 + 0.5
+        calls = [lambda p=p: kernels.delta_rule_scan(p[1], beta, decay, p[0], starts, slots, positions, out, wh, wh, wd, wd)
+                 for p in packs]
+        table[f"{label}_doderax_delta_rule_channel"] = timed(calls, 8.0 * tokens * wh * wd * wd, flops_peak) + note if prompt else \
+            timed(calls, rows * wh * wd * wd * 8 + tokens * wwidth * 24, hbm)
+        h = rand(tokens, width)
+        tail = torch.zeros(rows, width, device=device, dtype=f32)
+        mu = torch.rand(5, width, device=device, dtype=f32)
+        mixes = [torch.empty(5, tokens, width, device=device, dtype=bf16) for _ in range(2)]
+        calls = [lambda m=m: kernels.wkv_mix(h, tail, mu, row_of, starts, slots, positions, m, single_tokens_only=not prompt)
+                 for m in mixes]
+        table[f"{label}_wkv_mix"] = timed(calls, tokens * width * 12, hbm)
+        read = rand(tokens, wwidth, dtype=f32)
+        norm_weight = rand(wwidth, dtype=f32)
+        gated = torch.empty(tokens, wwidth, device=device, dtype=bf16)
+        calls = [lambda: kernels.gated_head_norm(read, h[:, :wwidth], norm_weight, gated, wh, wd, 1e-6, False)]
+        table[f"{label}_gated_head_norm"] = timed(calls, tokens * wwidth * 8, hbm)
+        # ---- two norms in one kernel beside one norm; the exact GELU beside the tanh form
+        residual = rand(tokens, width, dtype=f32)
+        w_a, w_b = rand(width, dtype=f32), rand(width, dtype=f32)
+        out_a, out_b = (torch.empty(tokens, width, device=device, dtype=bf16) for _ in range(2))
+        table[f"{label}_rms_norm_pair"] = timed([lambda: kernels.rms_norm_pair(residual, w_a, w_b, 1e-6, out_a, out_b)],
+                                                tokens * width * 8, hbm)
+        table[f"{label}_dense_rms_norm"] = timed([lambda: kernels.rms_norm(residual, w_a, 1e-6, out_a)], tokens * width * 6, hbm)
+        packs = copies(lambda: rand(tokens, s["ff"]), tokens * s["ff"] * 2)
+        table[f"{label}_gelu_erf"] = timed([lambda p=p: kernels.gelu_erf(p) for p in packs], tokens * s["ff"] * 4, hbm)
+        table[f"{label}_doderax_gelu_tanh"] = timed([lambda p=p: kernels.gelu_tanh(p) for p in packs], tokens * s["ff"] * 4, hbm)
+        # ---- routed experts, beside the dense decoder's products of the same work
+        experts, top, ff = s["experts"], s["top"], s["expert_ff"]
+        pairs = tokens * top
+        router = rand(experts + 8, width, scale=0.05)            # the router's rows, the shared gate's row, padding
+        correction = rand(experts, dtype=f32, scale=0.1)
+        logits = torch.empty(tokens, experts + 8, device=device, dtype=f32)
+        ids = torch.empty(tokens, top, device=device, dtype=i32)
+        weights = torch.empty(tokens, top, device=device, dtype=f32)
+        shared_gate = torch.empty(tokens, device=device, dtype=f32)
+        calls = [lambda: kernels.linear(h, router, logits, alloc=alloc)]
+        table[f"{label}_moe_router_logits"] = timed(calls, tokens * width * 2 + (experts + 8) * width * 2, hbm)
+        calls = [lambda: kernels.moe_route(logits, correction, True, ids, weights, shared_gate, experts, top,
+                                           s["groups"][0], s["groups"][1], 2.5)]
+        table[f"{label}_moe_route"] = timed(calls, tokens * (experts + 8) * 4, hbm)
+        tile = kernels.expert_tile_pairs(bf16, width, ff)
+        found = kernels.moe_sort(ids, experts, alloc, tile)
+        table[f"{label}_moe_sort"] = timed([lambda: kernels.moe_sort(ids, experts, alloc, tile)], pairs * 8, hbm)
+        torch.cuda.synchronize()
+        used = int(torch.unique(ids).numel())
+        banks = max(2, min(8, -(-(300 << 20) // (experts * ff * width * 6))))
+        gates = [rand(experts, ff, width, scale=0.03) for _ in range(banks)]
+        ups = [rand(experts, ff, width, scale=0.03) for _ in range(banks)]
+        downs = [rand(experts, width, ff, scale=0.03) for _ in range(banks)]
+        hidden = torch.empty(pairs, ff, device=device, dtype=bf16)
+        calls = [lambda g=g, u=u: kernels.moe_gate_up(h, found, top, g, u, hidden) for g, u in zip(gates, ups)]
+        table[f"{label}_moe_gate_up"] = timed(calls, 4.0 * pairs * ff * width, flops_peak) if prompt else \
+            timed(calls, used * 2 * ff * width * 2, hbm)
+        pair_rows = torch.empty(pairs, width, device=device, dtype=f32)
+        calls = [lambda d=d: kernels.moe_down(hidden, found, d, pair_rows) for d in downs]
+        table[f"{label}_moe_down"] = timed(calls, 2.0 * pairs * ff * width, flops_peak) if prompt else \
+            timed(calls, used * ff * width * 2, hbm)
+        shared_rows = rand(tokens, width, dtype=f32)
+        calls = [lambda: kernels.moe_combine(residual, pair_rows, weights, shared_rows, shared_gate)]
+        table[f"{label}_moe_combine"] = timed(calls, pairs * width * 4 + tokens * width * 12, hbm)
+        # the same work as dense products: a prompt's pairs as rows of one product; a step's experts as one wide matrix
+        dense_rows, dense_inter = (pairs, ff) if prompt else (tokens, ff * used)
+        x_dense = rand(dense_rows, width)
+        w_gu = [rand(2 * dense_inter, width, scale=0.03) for _ in range(max(2, min(8, -(-(300 << 20) // (dense_inter * width * 4)))))]
+        hidden_dense = torch.empty(dense_rows, dense_inter, device=device, dtype=bf16)
+        calls = [lambda w=w: kernels.gate_up_silu(x_dense, w, hidden_dense, alloc) for w in w_gu]
+        table[f"{label}_dense_gate_up_same_work"] = timed(calls, 4.0 * dense_rows * dense_inter * width, flops_peak) if prompt else \
+            timed(calls, 2 * dense_inter * width * 2, hbm)
+        w_d = [rand(width, dense_inter, scale=0.03) for _ in w_gu]
+        out_dense = torch.zeros(dense_rows, width, device=device, dtype=f32)
+        calls = [lambda w=w: kernels.linear(hidden_dense, w, out_dense, accumulate=True) for w in w_d]
+        table[f"{label}_dense_down_same_work"] = timed(calls, 2.0 * dense_rows * dense_inter * width, flops_peak) if prompt else \
+            timed(calls, dense_inter * width * 2, hbm)
+    return table
 
 
 def doderax_config(s: dict) -> dict:
@@ -264,6 +466,22 @@ def run(args, peaks: dict) -> dict:
                     table[f"{label}_{name}"] = timed(calls, read, hbm)
         return table
 
+    if args.design == "zufotar":
+        rand = lambda *shape, dtype=bf16, scale=1.0: (torch.randn(*shape, device=device, dtype=f32) * scale).to(dtype)
+        tools = {"timed": timed, "copies": copies, "rand": rand, "device": device, "hbm": hbm, "flops_peak": flops_peak}
+        report = {}
+        for name in [n for n in ZUFOTAR_SIZES if args.design_sizes in ("all", n)]:
+            s = ZUFOTAR_SIZES[name]
+            entry = {"sizes": s}
+            if not args.skip_points:
+                entry["kernels_us_and_fraction_of_roofline"] = zufotar_kernel_table(s, tools)
+                torch.cuda.empty_cache()
+            beside = dict(s, layers=s["runs"])
+            entry["zufotar"] = model_numbers(zufotar_config(s), s["vocab"])
+            entry["doderax"] = model_numbers(doderax_config(beside), s["vocab"])
+            entry["dense_swiglu"] = model_numbers(dense_config(beside), s["vocab"])
+            report[name] = entry
+        return report
     chosen = [name for name in DESIGN_SIZES if args.design_sizes in ("all", name)]
     report = {}
     for name in chosen:

@@ -99,3 +99,80 @@ MIR_EXPORT int mir_gemm_bf16_lt(const void* x, int ldx, const void* w, int ldw, 
   mir_count_launch("gemm_bf16_lt");
   return MIR_OK;
 }
+
+namespace {
+
+struct BatchedPlan {
+  cublasLtMatmulDesc_t op = nullptr;
+  cublasLtMatrixLayout_t w = nullptr, x = nullptr, c = nullptr;
+  cublasLtMatmulAlgo_t algo;
+};
+using BatchedKey = std::tuple<int, int, int, int, int, int, long long, long long, long long, size_t>;
+std::map<BatchedKey, BatchedPlan> g_batched_plans;
+
+int make_batched_plan(int m, int n, int k, int batch, int ldx, int ldo, long long x_stride, long long w_stride,
+                      long long o_stride, size_t workspace, BatchedPlan& plan) {
+  LT_CHECK(cublasLtMatmulDescCreate(&plan.op, CUBLAS_COMPUTE_32F, CUDA_R_32F));
+  const cublasOperation_t none = CUBLAS_OP_N;
+  LT_CHECK(cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_TRANSA, &none, sizeof(none)));
+  LT_CHECK(cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_TRANSB, &none, sizeof(none)));
+  // column-major terms: C[n, m] = W[n, k] . X[k, m]; w is stored [k, n] row-major, which is [n, k] column-major
+  LT_CHECK(cublasLtMatrixLayoutCreate(&plan.w, CUDA_R_16BF, n, k, n));
+  LT_CHECK(cublasLtMatrixLayoutCreate(&plan.x, CUDA_R_16BF, k, m, ldx));
+  LT_CHECK(cublasLtMatrixLayoutCreate(&plan.c, CUDA_R_16BF, n, m, ldo));
+  const int32_t count = batch;
+  const int64_t strides[3] = {w_stride, x_stride, o_stride};
+  cublasLtMatrixLayout_t layouts[3] = {plan.w, plan.x, plan.c};
+  for (int i = 0; i < 3; ++i) {
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(layouts[i], CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &count, sizeof(count)));
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(layouts[i], CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &strides[i],
+                                              sizeof(strides[i])));
+  }
+  cublasLtMatmulPreference_t preference = nullptr;
+  LT_CHECK(cublasLtMatmulPreferenceCreate(&preference));
+  LT_CHECK(cublasLtMatmulPreferenceSetAttribute(preference, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &workspace,
+                                                sizeof(workspace)));
+  cublasLtMatmulHeuristicResult_t result;
+  int found = 0;
+  const cublasStatus_t status = cublasLtMatmulAlgoGetHeuristic(g_handle, plan.op, plan.w, plan.x, plan.c, plan.c,
+                                                               preference, 1, &result, &found);
+  cublasLtMatmulPreferenceDestroy(preference);
+  if (status != CUBLAS_STATUS_SUCCESS || found == 0) {
+    mir_set_error("cuBLASLt has no algorithm for %d products of m %d n %d k %d (status %d)", batch, m, n, k, (int)status);
+    return MIR_LIBRARY_ERROR;
+  }
+  plan.algo = result.algo;
+  return MIR_OK;
+}
+
+}  // namespace
+
+// `batch` products at once: out_b[M, N] = x_b[M, K] . w_b[K, N] with x_b = x + b * x_stride (row stride ldx), w_b = w
+// + b * K * N (row-major [K, N], contiguous), out_b = out + b * o_stride (row stride ldo); all bf16, 32-bit
+// accumulation.  The products per head of a mixer: b walks over the heads of [tokens, heads, width] views.
+MIR_EXPORT int mir_gemm_bf16_lt_batched(const void* x, int ldx, long long x_stride, const void* w, void* out, int ldo,
+                                        long long o_stride, int m, int n, int k, int batch, void* workspace,
+                                        size_t workspace_bytes, cudaStream_t stream) {
+  if (m == 0 || n == 0 || batch == 0) return MIR_OK;
+  if (m < 0 || n < 0 || k <= 0 || batch < 0) {
+    mir_set_error("gemm_bf16_batched: bad sizes m %d n %d k %d batch %d", m, n, k, batch);
+    return MIR_BAD_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_handle) LT_CHECK(cublasLtCreate(&g_handle));
+  const long long w_stride = (long long)k * n;
+  const BatchedKey key(m, n, k, batch, ldx, ldo, x_stride, w_stride, o_stride, workspace_bytes);
+  auto it = g_batched_plans.find(key);
+  if (it == g_batched_plans.end()) {
+    BatchedPlan plan;
+    const int status = make_batched_plan(m, n, k, batch, ldx, ldo, x_stride, w_stride, o_stride, workspace_bytes, plan);
+    if (status != MIR_OK) return status;
+    it = g_batched_plans.emplace(key, plan).first;
+  }
+  BatchedPlan& plan = it->second;
+  const float alpha = 1.0f, beta = 0.0f;
+  LT_CHECK(cublasLtMatmul(g_handle, plan.op, &alpha, w, plan.w, x, plan.x, &beta, out, plan.c, out, plan.c, &plan.algo,
+                          workspace, workspace_bytes, stream));
+  mir_count_launch("gemm_bf16_lt_batched");
+  return MIR_OK;
+}

@@ -60,7 +60,7 @@ struct StreamNorm {
   float* best_value;         // float32 epilogue (the output head): [m][best_stride] the largest finite result of every
   int* best_index;           //   32 columns (entry 4 x tile + warp) and its column, ties to the lower column; or null
   int best_stride;
-  int activation;            // store epilogue: 0 none, 1 the tanh GELU of the result
+  int activation;            // store epilogue: 0 none, 1 the tanh GELU of the result, 2 the exact (erf) GELU
 };
 
 // (Shared memory lets three CTAs share an SM; the registers are capped as if six did: 56 instead of up to 95 per
@@ -314,6 +314,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 float t;
                 asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * result * result, result, result)));
                 stored = 0.5f * result * (1.0f + t);
+              } else if (norm.activation == 2) {              // 0.5 z (1 + erf(z / sqrt 2))
+                stored = 0.5f * result * (1.0f + erff(result * 0.70710678118654752f));
               }
               reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(stored);
             } else {
@@ -446,7 +448,8 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
                                        int sumsq_tiles, float eps, float* sumsq_out, const float* next_weight,
                                        void* weighted_out, int ld_weighted, cudaStream_t stream) {
   if (m == 0 || n == 0) return MIR_OK;
-  const bool gelu = mode == 4;                                 // mode 4: the store epilogue with the tanh GELU, no bias
+  const bool gelu = mode == 4 || mode == 5;                    // modes 4, 5: the store epilogue with the tanh / exact GELU, no bias
+  const int activation = mode == 4 ? 1 : (mode == 5 ? 2 : 0);
   if (gelu) {
     if (bias) { mir_set_error("tc_stream: the GELU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
     mode = STORE;
@@ -482,7 +485,7 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
   norm.best_value = nullptr;
   norm.best_index = nullptr;
   norm.best_stride = 0;
-  norm.activation = gelu ? 1 : 0;
+  norm.activation = activation;
   switch (mode) {
     case STORE: return launch<STORE>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
     case ACCUM: return launch<ACCUM>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);

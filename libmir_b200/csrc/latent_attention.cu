@@ -137,7 +137,35 @@ __global__ void head_linear_kernel(const T* __restrict__ x, long long x_token, l
   out[(size_t)token * out_token + (size_t)head * out_head + o] = from_float<T>(acc);
 }
 
+// x[t, c] *= sigmoid(gate[t, c]) on rows with strides, in place; the product was rounded to the activations' type
+// before, as a projection is.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, long long x_stride, const T* __restrict__ gate, long long gate_stride,
+                                    int columns, size_t total) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const size_t row = index / columns;
+  const int c = (int)(index - row * columns);
+  T* at = x + row * x_stride + c;
+  *at = from_float<T>(to_float(*at) * sigmoid_of(to_float(gate[row * gate_stride + c])));
+}
+
 }  // namespace
+
+MIR_EXPORT int mir_sigmoid_gate(int bf16, void* x, long long x_stride, const void* gate, long long gate_stride, int rows,
+                                int columns, cudaStream_t stream) {
+  if (rows == 0 || columns == 0) return MIR_OK;
+  if (rows < 0 || columns < 0) { mir_set_error("sigmoid_gate: bad sizes"); return MIR_BAD_ARGUMENT; }
+  const size_t total = (size_t)rows * columns;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (bf16)
+    return mir_launch("sigmoid_gate", sigmoid_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 0, (__nv_bfloat16*)x,
+                      x_stride, (const __nv_bfloat16*)gate, gate_stride, columns, total);
+  return mir_launch("sigmoid_gate", sigmoid_gate_kernel<float>, grid, dim3(256), 0, stream, 0, (float*)x, x_stride,
+                    (const float*)gate, gate_stride, columns, total);
+}
 
 MIR_EXPORT int mir_latent_prepare(int bf16, const void* packed, long long ld, int q_offset, int q_rank, int kv_offset,
                                   int kv_rank, int rotary, const float* q_norm, const float* kv_norm, float eps,

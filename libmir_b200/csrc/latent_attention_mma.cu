@@ -117,6 +117,7 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[mt][nt][e] = 0.0f;
   const int first_column = warp * NT * 8;
+  const int row_tiles = (min(kRows, pairs - first_pair) + 15) / 16;   // tiles of 16 query rows that hold any row
 
   for (int k0 = key_begin; k0 < key_end; k0 += kKeys) {
     __syncthreads();                                             // the tile before is done with (and q_s is written)
@@ -146,9 +147,11 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         ldmatrix_x2(b, b_at + k);
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) {
-          unsigned a[4];
-          ldmatrix_x4(a, a_at + (size_t)mt * 16 * ld + k);
-          mma_bf16(s[mt], a, b);
+          if (mt < row_tiles) {                                   // (decoded tokens: heads / 16 of the four)
+            unsigned a[4];
+            ldmatrix_x4(a, a_at + (size_t)mt * 16 * ld + k);
+            mma_bf16(s[mt], a, b);
+          }
         }
       }
       const int g = lane >> 2, c = warp * 8 + (lane & 3) * 2;
@@ -210,14 +213,16 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
       for (int k = 0; k < kKeys; k += 16) {
         unsigned a[4][4];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) ldmatrix_x4(a[mt], a_at + mt * 16 * ldp + k);
+        for (int mt = 0; mt < 4; ++mt)
+          if (mt < row_tiles) ldmatrix_x4(a[mt], a_at + mt * 16 * ldp + k);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           if (first_column + nt * 8 < rank) {
             unsigned b[2];
             ldmatrix_x2_trans(b, b_at + (size_t)k * ld + nt * 8);
 #pragma unroll
-            for (int mt = 0; mt < 4; ++mt) mma_bf16(o[mt][nt], a[mt], b);
+            for (int mt = 0; mt < 4; ++mt)
+              if (mt < row_tiles) mma_bf16(o[mt][nt], a[mt], b);
           }
         }
       }

@@ -1,7 +1,8 @@
 // Kernels of a mixture of gated experts.  P = tokens * top pairs of (token, chosen expert); pair p = token * top + slot.
 //
-//   moe_route     per token: 32-bit router logits, sigmoid scores, choice among the experts of the best groups by
-//                 score + correction, weights = chosen scores / their sum * scale; and the shared expert's gate
+//   moe_route     per token, from the router's 32-bit logits (a product of the framework): sigmoid scores, choice among
+//                 the experts of the best groups by score + correction, weights = chosen scores / their sum * scale;
+//                 and the shared expert's gate
 //   moe_sort      the pairs ordered by expert (a stable counting sort inside one CTA), each expert's range, and the
 //                 list of tiles (8 or 64 pairs of one expert) that the grouped products walk over
 //   moe_grouped   products on the sorted pairs with each pair's own expert's weights: hidden = silu(Wg x) * (Wu x)
@@ -22,76 +23,92 @@ constexpr int kMaxExperts = 1024;
 
 __device__ __forceinline__ float sigmoid_of(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// One CTA per token.  Shared memory: score[E] | choice[E] | group score[groups].
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
-                                 const float* __restrict__ correction, const float* __restrict__ shared_gate_w,
-                                 int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ shared_gate,
-                                 int width, int experts, int top, int groups, int keep, float scale) {
+// One warp per token, four tokens a CTA.  logits [tokens, >= experts (+ 1)] 32-bit: the router's logits and, behind
+// them, the shared expert's gate logit (has_gate).  Shared memory per warp: score[E] | choice[E] | group score[groups].
+// Among equal scores the expert (or group) with the lower index wins.
+constexpr int kRouteWarps = 4;
+
+__device__ __forceinline__ void warp_best(float& value, int& index, bool want_max) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, value, o);
+    const int other_index = __shfl_xor_sync(0xffffffffu, index, o);
+    const bool better = want_max ? (other > value || (other == value && other_index < index))
+                                 : (other < value || (other == value && other_index > index));
+    if (other_index >= 0 && (index < 0 || better)) { value = other; index = other_index; }
+  }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
+                                 int has_gate, int* __restrict__ ids, float* __restrict__ weights,
+                                 float* __restrict__ shared_gate, int tokens, int experts, int top, int groups, int keep,
+                                 float scale) {
   extern __shared__ float route_shared[];
-  float* score = route_shared;
-  float* choice = route_shared + experts;
-  float* group_score = route_shared + 2 * experts;
   grid_launch_dependents();
   grid_dependency_wait();
-  const int token = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const T* x = h + (size_t)token * ld;
-  for (int e = warp; e < experts + (shared_gate_w != nullptr ? 1 : 0); e += warps) {
-    const float* w = e < experts ? router + (size_t)e * width : shared_gate_w;
-    float sum = 0.0f;
-    for (int c = lane; c < width; c += 32) sum = fmaf(to_float(x[c]), w[c], sum);
-    sum = warp_sum(sum);
-    if (lane == 0) {
-      const float s = sigmoid_of(sum);
-      if (e < experts) {
-        score[e] = s;
-        choice[e] = correction != nullptr ? s + correction[e] : s;
-      } else {
-        shared_gate[token] = s;
-      }
-    }
+  const int lane = threadIdx.x, warp = threadIdx.y;
+  const int token = blockIdx.x * kRouteWarps + warp;
+  if (token >= tokens) return;
+  float* score = route_shared + (size_t)warp * (2 * experts + groups);
+  float* choice = score + experts;
+  float* group_score = choice + experts;
+  const float* z = logits + (size_t)token * ld;
+  for (int e = lane; e < experts; e += 32) {
+    const float s = sigmoid_of(z[e]);
+    score[e] = s;
+    choice[e] = correction != nullptr ? s + correction[e] : s;
   }
-  __syncthreads();
+  if (has_gate && lane == 0) shared_gate[token] = sigmoid_of(z[experts]);
+  __syncwarp();
   const int per_group = experts / groups;
-  // a group's score: the sum of its two largest choice scores (of its one score where a group is one expert)
-  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
-    float first = -FLT_MAX, second = -FLT_MAX;
-    for (int e = g * per_group; e < (g + 1) * per_group; ++e) {
-      const float c = choice[e];
-      if (c > first) { second = first; first = c; }
-      else if (c > second) second = c;
-    }
-    group_score[g] = per_group > 1 ? first + second : first;
-  }
-  __syncthreads();
-  if (threadIdx.x != 0) return;
-  // experts of all but the `keep` best groups cannot be chosen: their choice scores count as minus infinity
   if (keep < groups) {
+    // a group's score: the sum of its two largest choice scores (of its one score where a group is one expert)
+    for (int g = lane; g < groups; g += 32) {
+      float first = -FLT_MAX, second = -FLT_MAX;
+      for (int e = g * per_group; e < (g + 1) * per_group; ++e) {
+        const float c = choice[e];
+        if (c > first) { second = first; first = c; }
+        else if (c > second) second = c;
+      }
+      group_score[g] = per_group > 1 ? first + second : first;
+    }
+    __syncwarp();
+    // experts of all but the `keep` best groups cannot be chosen: their choice scores count as minus infinity
     for (int round = 0; round < groups - keep; ++round) {
-      int worst = -1;
       float low = FLT_MAX;
-      for (int g = groups - 1; g >= 0; --g)                      // among equals the later group goes first
-        if (group_score[g] != FLT_MAX && group_score[g] < low) { low = group_score[g]; worst = g; }
+      int worst = -1;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = group_score[g];
+        if (v != FLT_MAX && (worst < 0 || v <= low)) { low = v; worst = g; }     // (among equals the later group goes)
+      }
+      warp_best(low, worst, false);
       if (worst < 0) break;
-      group_score[worst] = FLT_MAX;                              // marked as dropped
-      for (int e = worst * per_group; e < (worst + 1) * per_group; ++e) choice[e] = -FLT_MAX;
+      if (lane == 0) group_score[worst] = FLT_MAX;                // marked as dropped
+      for (int e = worst * per_group + lane; e < (worst + 1) * per_group; e += 32) choice[e] = -FLT_MAX;
+      __syncwarp();
     }
   }
   float total = 0.0f;
   for (int slot = 0; slot < top; ++slot) {
-    int best = -1;
     float high = -FLT_MAX;
-    for (int e = 0; e < experts; ++e)
-      if (choice[e] > high) { high = choice[e]; best = e; }
+    int best = -1;
+    for (int e = lane; e < experts; e += 32) {
+      const float c = choice[e];
+      if (c > high) { high = c; best = e; }
+    }
+    if (best >= 0 && high == -FLT_MAX) best = -1;
+    warp_best(high, best, true);
     if (best < 0) best = 0;                                      // (fewer choosable experts than top: not a valid model)
-    choice[best] = -FLT_MAX;
-    ids[(size_t)token * top + slot] = best;
-    weights[(size_t)token * top + slot] = score[best];
+    if (lane == 0) {
+      choice[best] = -FLT_MAX;
+      ids[(size_t)token * top + slot] = best;
+      weights[(size_t)token * top + slot] = score[best];
+    }
     total += score[best];
+    __syncwarp();
   }
   const float factor = scale / (total + 1e-20f);
-  for (int slot = 0; slot < top; ++slot) weights[(size_t)token * top + slot] *= factor;
+  for (int slot = lane; slot < top; slot += 32) weights[(size_t)token * top + slot] *= factor;
 }
 
 // One CTA of 1024 threads.  order[i] = the i-th pair when the pairs are sorted by expert (pairs of one expert stay in
@@ -248,6 +265,7 @@ constexpr int kMmaTile = 64;          // pairs of one expert per CTA
 constexpr int kMmaColumns = 64;       // outputs per CTA
 constexpr int kMmaStep = 32;          // inputs per stage
 constexpr int kMmaLd = kMmaStep + 8;  // row stride in shared memory: 80 bytes, so that ldmatrix meets no bank twice
+constexpr int kMmaStages = 3;         // a ring of three stages: two loads are in flight while one is multiplied
 
 __device__ __forceinline__ void mma_ldmatrix_x4(unsigned (&r)[4], const void* p) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(p);
@@ -278,8 +296,8 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const
                        long long ldo, const int* __restrict__ scatter, const int* __restrict__ tiles,
                        const int* __restrict__ tile_count, const int* __restrict__ offsets, int K, int N) {
   constexpr int WEIGHT_ROWS = GATED ? 2 * kMmaColumns : kMmaColumns;
-  __shared__ __align__(16) __nv_bfloat16 a_s[2][kMmaTile][kMmaLd];
-  __shared__ __align__(16) __nv_bfloat16 b_s[2][WEIGHT_ROWS][kMmaLd];
+  __shared__ __align__(16) __nv_bfloat16 a_s[kMmaStages][kMmaTile][kMmaLd];
+  __shared__ __align__(16) __nv_bfloat16 b_s[kMmaStages][WEIGHT_ROWS][kMmaLd];
   __shared__ int source[kMmaTile];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -316,10 +334,14 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const
       if (GATED) acc_b[nt][e] = 0.0f;
     }
   stage_in(0, 0);
+  if (kMmaStep < K) stage_in(1, kMmaStep);
   int stage = 0;
-  for (int k0 = 0; k0 < K; k0 += kMmaStep, stage ^= 1) {
-    if (k0 + kMmaStep < K) {
-      stage_in(stage ^ 1, k0 + kMmaStep);
+  for (int k0 = 0; k0 < K; k0 += kMmaStep, stage = (stage + 1) % kMmaStages) {
+    // the stage after next is the one that was multiplied last: every warp is past it (the barrier below)
+    if (k0 + 2 * kMmaStep < K) {
+      stage_in((stage + 2) % kMmaStages, k0 + 2 * kMmaStep);
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+    } else if (k0 + kMmaStep < K) {
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -340,7 +362,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const
         }
       }
     }
-    __syncthreads();                                             // the stage is free for the step after next
+    __syncthreads();                                             // the stage is free for the load two steps on
   }
   const int g = lane >> 2, c2 = (lane & 3) * 2;
 #pragma unroll
@@ -404,25 +426,23 @@ int launch_grouped(cudaStream_t stream, const void* x, long long ldx, const int*
 
 }  // namespace
 
-// h [tokens, width] (row stride ld) in the activations' type; router [experts, width], correction [experts] (or
-// null), shared_gate_w [width] (or null) 32-bit; ids, weights [tokens, top]; shared_gate [tokens].
-MIR_EXPORT int mir_moe_route(int bf16, const void* h, long long ld, const float* router, const float* correction,
-                             const float* shared_gate_w, int* ids, float* weights, float* shared_gate, int tokens,
-                             int width, int experts, int top, int groups, int keep, float scale, cudaStream_t stream) {
+// logits [tokens, >= experts + has_gate] 32-bit with row stride ld: the router's logits (and the shared expert's gate
+// logit behind them); correction [experts] (or null) 32-bit; ids, weights [tokens, top]; shared_gate [tokens].
+MIR_EXPORT int mir_moe_route(const float* logits, long long ld, const float* correction, int has_gate, int* ids,
+                             float* weights, float* shared_gate, int tokens, int experts, int top, int groups, int keep,
+                             float scale, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
-  if (tokens < 0 || width <= 0 || experts <= 0 || experts > kMaxExperts || top <= 0 || top > experts || groups <= 0 ||
-      experts % groups || keep <= 0 || keep > groups || (long long)keep * (experts / groups) < top) {
+  if (tokens < 0 || experts <= 0 || experts > kMaxExperts || top <= 0 || top > experts || groups <= 0 ||
+      experts % groups || keep <= 0 || keep > groups || (long long)keep * (experts / groups) < top ||
+      (has_gate && shared_gate == nullptr)) {
     mir_set_error("moe_route: bad sizes (tokens %d, experts %d, top %d, groups %d of which %d are kept)", tokens, experts,
                   top, groups, keep);
     return MIR_BAD_ARGUMENT;
   }
-  const size_t smem = (size_t)(2 * experts + groups) * sizeof(float);
-  if (bf16)
-    return mir_launch("moe_route", moe_route_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, stream, 0,
-                      (const __nv_bfloat16*)h, ld, router, correction, shared_gate_w, ids, weights, shared_gate, width,
-                      experts, top, groups, keep, scale);
-  return mir_launch("moe_route", moe_route_kernel<float>, dim3(tokens), dim3(128), smem, stream, 0, (const float*)h, ld,
-                    router, correction, shared_gate_w, ids, weights, shared_gate, width, experts, top, groups, keep, scale);
+  const size_t smem = (size_t)kRouteWarps * (2 * experts + groups) * sizeof(float);
+  return mir_launch("moe_route", moe_route_kernel, dim3((tokens + kRouteWarps - 1) / kRouteWarps), dim3(32, kRouteWarps),
+                    smem, stream, 0, logits, ld, correction, has_gate, ids, weights, shared_gate, tokens, experts, top,
+                    groups, keep, scale);
 }
 
 // How many tiles of tile_pairs pairs there can be at most for `pairs` pairs over `experts` experts (`tiles` holds two

@@ -57,7 +57,8 @@ __global__ void wkv_tail_kernel(const T* __restrict__ h, long long ld, float* __
 }
 
 constexpr int kScanWarps = 4;
-constexpr int kScanChunk = 16;
+constexpr int kScanChunkNarrow = 32;                              // tokens staged at a time: heads up to 64 wide,
+constexpr int kScanChunkWide = 16;                                // and wider ones (the stage stays under 48 KB)
 constexpr int kLanes = 8;                                        // lanes that share one column of the state
 
 // blockDim (32, kScanWarps), grid (rows, heads, ceil(dim / (kScanWarps * 4))).  Lane l of a column holds the key
@@ -74,6 +75,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   constexpr int BLOCK_COLUMNS = COLUMNS * kScanWarps;
   constexpr int PADDED = kLanes * PER;
   constexpr int ROW = 3 * PADDED + 4 + BLOCK_COLUMNS;            // r | k | decay | bonus term | v of this CTA's columns
+  constexpr int kScanChunk = PER <= 8 ? kScanChunkNarrow : kScanChunkWide;
   __shared__ __align__(16) float staged[kScanChunk * ROW];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -108,30 +110,29 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   for (int from = start; from < end; from += kScanChunk) {
     const int count = min(kScanChunk, end - from);
     __syncthreads();                                             // the chunk before has been read
-    for (int index = thread; index < count * PADDED; index += kScanWarps * 32) {
-      const int t = index / PADDED, i = index - t * PADDED;
+    // a warp stages whole tokens: r, k and the decay exp(-exp(z + w0)) of every channel, and the token's bonus term
+    // sum_i r_i u_i k_i, which is the same for every column of the head
+    for (int t = warp; t < count; t += kScanWarps) {
       float* at = staged + t * ROW;
-      if (i < dim) {
-        const size_t source = (size_t)(from + t) * ld + head_at + i;
-        at[i] = to_float(r[source]);
-        at[PADDED + i] = to_float(k[source]);
-        at[2 * PADDED + i] = expf(-expf(decay_raw[(size_t)(from + t) * width + head_at + i] + decay_bias[head_at + i]));
-      } else {
-        at[i] = 0.0f; at[PADDED + i] = 0.0f; at[2 * PADDED + i] = 0.0f;
+      float sum = 0.0f;
+      for (int i = lane; i < PADDED; i += 32) {
+        float rr = 0.0f, kk = 0.0f, ww = 0.0f;
+        if (i < dim) {
+          const size_t source = (size_t)(from + t) * ld + head_at + i;
+          rr = to_float(r[source]);
+          kk = to_float(k[source]);
+          ww = expf(-expf(decay_raw[(size_t)(from + t) * width + head_at + i] + decay_bias[head_at + i]));
+          sum = fmaf(rr * bonus[head_at + i], kk, sum);
+        }
+        at[i] = rr; at[PADDED + i] = kk; at[2 * PADDED + i] = ww;
       }
+      sum = warp_sum(sum);
+      if (lane == 0) at[3 * PADDED] = sum;
     }
     for (int index = thread; index < count * BLOCK_COLUMNS; index += kScanWarps * 32) {
       const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
       staged[t * ROW + 3 * PADDED + 4 + c] =
           first_column + c < dim ? to_float(v[(size_t)(from + t) * ld + head_at + first_column + c]) : 0.0f;
-    }
-    __syncthreads();
-    for (int t = warp; t < count; t += kScanWarps) {             // the bonus term sum_i r_i u_i k_i of each token
-      const float* at = staged + t * ROW;
-      float sum = 0.0f;
-      for (int i = lane; i < dim; i += 32) sum = fmaf(at[i] * bonus[head_at + i], at[PADDED + i], sum);
-      sum = warp_sum(sum);
-      if (lane == 0) staged[t * ROW + 3 * PADDED] = sum;
     }
     __syncthreads();
     const float* in = staged - ROW;

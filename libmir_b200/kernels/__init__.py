@@ -56,14 +56,15 @@ _SIGNATURES = {
                                c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
         "mir_rope_rows": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
                           c_float, c_int, c_int, c_int, c_int, c_void_p],
+        "mir_sigmoid_gate": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p],
         "mir_head_linear": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p,
                             c_longlong, c_int, c_int, c_int, c_int, c_void_p],
         "mir_wkv_mix": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_void_p],
         "mir_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "mir_moe_route": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                          c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "mir_moe_route": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                          c_int, c_float, c_void_p],
         "mir_moe_tile_slots": [c_int, c_int, c_int],
         "mir_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "mir_moe_gate_up": [c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -130,6 +131,8 @@ _SIGNATURES = {
                                       c_void_p],
         "mir_set_option": [ctypes.c_char_p, c_int],
         "mir_get_option": [ctypes.c_char_p],
+        "mir_gemm_bf16_lt_batched": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int,
+                                     c_int, c_void_p, c_size_t, c_void_p],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
     },
@@ -603,10 +606,15 @@ def rope_rows(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, inv
                                   float(magnitude), int(interleaved), tokens, heads, rotary, _stream()))
 
 
+HEAD_LINEAR_LIBRARY = True       # False: the products per head always run the 32-bit multiply-add kernel
+
+
 def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
     """out[t, h, :] = weight[h]^T x[t, h, :] for weight [heads, in, out] (a product per head; 32-bit accumulation),
     times sigmoid(gate[t, h, :]) if a gate [tokens, heads * out] (unit column stride) is given.  x [tokens, heads, in]
-    and out [tokens, heads, out] are views with unit stride in the last dimension."""
+    and out [tokens, heads, out] are views with unit stride in the last dimension.  bfloat16 views whose rows and
+    heads start on 16-byte boundaries run as one batched library product (the heads are the batch) followed by the
+    gate's kernel; everything else runs our kernel, in which every output is one ascending chain."""
     _cuda(x, weight, out, gate)
     tokens, heads, in_dim = x.shape
     out_dim = weight.shape[2]
@@ -616,6 +624,20 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: 
     if gate is not None:
         _require(gate.shape == (tokens, heads * out_dim) and gate.stride(1) == 1 and gate.dtype == x.dtype,
                  "head_linear: the gate is [tokens, heads * out] in the activations' dtype")
+    aligned = all(v % 8 == 0 for v in (in_dim, out_dim, x.stride(0), x.stride(1), out.stride(0), out.stride(1))) \
+        and x.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+    if HEAD_LINEAR_LIBRARY and x.dtype == torch.bfloat16 and aligned and tokens > 0:
+        lib = library("bf16")
+        workspace = _lt_workspace(x.device)
+        _check(lib, lib.mir_gemm_bf16_lt_batched(x.data_ptr(), x.stride(0), x.stride(1), weight.data_ptr(), out.data_ptr(),
+                                                 out.stride(0), out.stride(1), tokens, out_dim, in_dim, heads,
+                                                 workspace.data_ptr(), workspace.numel(), _stream()))
+        if gate is not None:
+            _require(out.stride(1) == out_dim, "head_linear: a gated result has its heads side by side")
+            core = library("core")
+            _check(core, core.mir_sigmoid_gate(1, out.data_ptr(), out.stride(0), gate.data_ptr(), gate.stride(0), tokens,
+                                               heads * out_dim, _stream()))
+        return
     lib = library("core")
     _check(lib, lib.mir_head_linear(_is_bf16(x), x.data_ptr(), x.stride(0), x.stride(1), weight.data_ptr(), out.data_ptr(),
                                     out.stride(0), out.stride(1), _ptr(gate), gate.stride(0) if gate is not None else 0,
@@ -721,29 +743,25 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_raw: torch
 
 
 # --------------------------------------------------------------------------- routed experts
-def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor],
-              shared_gate_weight: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor,
-              shared_gate: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float) -> None:
-    """Per token: scores = sigmoid(router h) in 32-bit; the `top` experts with the largest score + correction among
-    the experts of the `keep` best of `groups` groups of neighbours (a group's score: the sum of its two largest
-    score + correction) -> ids [tokens, top]; weights [tokens, top] = their scores / their sum * scale;
-    shared_gate[t] = sigmoid(shared_gate_weight . h) if given."""
-    _cuda(h, router, correction, shared_gate_weight, ids, weights, shared_gate)
-    tokens, width = h.shape
-    experts = router.shape[0]
-    _require(h.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == width
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], has_gate: bool, ids: torch.Tensor,
+              weights: torch.Tensor, shared_gate: Optional[torch.Tensor], experts: int, top: int, groups: int, keep: int,
+              scale: float) -> None:
+    """Per token, from the router's 32-bit logits [tokens, >= experts (+ 1)]: scores = sigmoid(logits); the `top`
+    experts with the largest score + correction among the experts of the `keep` best of `groups` groups of neighbours
+    (a group's score: the sum of its two largest score + correction) -> ids [tokens, top]; weights [tokens, top] =
+    their scores / their sum * scale; with has_gate, shared_gate[t] = sigmoid(logits[t, experts])."""
+    _cuda(logits, correction, ids, weights, shared_gate)
+    tokens = logits.shape[0]
+    _require(logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts + int(has_gate)
              and (correction is None or (correction.dtype == torch.float32 and correction.numel() == experts))
              and ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (tokens, top)
-             and weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == (tokens, top),
-             "moe_route: shapes or dtypes do not fit")
-    if shared_gate_weight is not None:
-        _require(shared_gate_weight.dtype == torch.float32 and shared_gate_weight.numel() == width
-                 and shared_gate_weight.is_contiguous() and shared_gate is not None and shared_gate.dtype == torch.float32
-                 and shared_gate.numel() >= tokens, "moe_route: the shared gate is a float32 vector of the width")
+             and weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == (tokens, top)
+             and (not has_gate or (shared_gate is not None and shared_gate.dtype == torch.float32
+                                   and shared_gate.numel() >= tokens)), "moe_route: shapes or dtypes do not fit")
     lib = library("core")
-    _check(lib, lib.mir_moe_route(_is_bf16(h), h.data_ptr(), h.stride(0), router.data_ptr(), _ptr(correction),
-                                  _ptr(shared_gate_weight), ids.data_ptr(), weights.data_ptr(), _ptr(shared_gate), tokens,
-                                  width, experts, top, groups, keep, float(scale), _stream()))
+    _check(lib, lib.mir_moe_route(logits.data_ptr(), logits.stride(0), _ptr(correction), int(has_gate), ids.data_ptr(),
+                                  weights.data_ptr(), _ptr(shared_gate), tokens, experts, top, groups, keep, float(scale),
+                                  _stream()))
 
 
 class ExpertOrder:
@@ -1207,8 +1225,9 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
     return bool(wrote.value)
 
 
-def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None) -> None:
-    """out = gelu_tanh(x . weight^T) in the activations' dtype.  bfloat16: one kernel with the activation in its
+def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None, exact: bool = False) -> None:
+    """out = gelu(x . weight^T) in the activations' dtype: the tanh form, or with `exact` 0.5 z (1 + erf(z / sqrt 2))
+    (computed with erff, in the epilogue too).  bfloat16: one kernel with the activation in its
     epilogue where our tcgen05 products take the rows (up to few_rows_max on the weight-streaming kernel, where x may
     be a NormedResidual, a norm folded into this product; from tensor_core_min_rows on the many-rows kernel; the
     approximate hardware tanh, whose error is below bfloat16's rounding), else the library product and the activation
@@ -1222,21 +1241,25 @@ def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None) -> None:
             and rows.stride(0) % 8 == 0 and rows.data_ptr() % 16 == 0 and rows.stride(1) == 1 and out.stride(1) == 1
             and weight.is_contiguous() and out.shape == (m, n) and FUSE_GELU_INTO_PRODUCT):
         lib = library("bf16")
+        mode = MODE_GELU_ERF if exact else MODE_GELU
         if 0 < m <= min(get_option("few_rows_max"), STREAM_MAX_ROWS) and (lazy is None or m <= NORM_STAT_STRIDE):
             _check(lib, lib.mir_gemm_tc_stream_bf16(
-                MODE_GELU, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None, out.data_ptr(), out.stride(0), m, n,
+                mode, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None, out.data_ptr(), out.stride(0), m, n,
                 k, 0, lazy.sumsq.data_ptr() if lazy is not None else None, lazy.tiles if lazy is not None else 0,
                 lazy.eps if lazy is not None else 0.0, None, None, None, 0, _stream()))
             return
         if lazy is None and m >= get_option("tensor_core_min_rows"):
-            _check(lib, lib.mir_gemm_tc_bf16(MODE_GELU, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None,
+            _check(lib, lib.mir_gemm_tc_bf16(mode, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None,
                                              out.data_ptr(), out.stride(0), m, n, k, 0, _stream()))
             return
     if lazy is not None:
         x = lazy.materialize(alloc)
     linear(x, weight, out, alloc=alloc)
     _require(out.is_contiguous(), "linear_gelu: a contiguous result is needed")
-    gelu_tanh(out)
+    if exact:
+        gelu_erf(out)
+    else:
+        gelu_tanh(out)
 
 
 def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
@@ -1317,7 +1340,7 @@ def tensor_core_linear_error() -> int:
 
 
 NORM_STAT_STRIDE = 32        # tokens per row of the sums-of-squares arrays (kNormStatStride of the kernels)
-MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU, MODE_GELU = 0, 1, 2, 3, 4
+MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU, MODE_GELU, MODE_GELU_ERF = 0, 1, 2, 3, 4, 5
 
 
 def few_rows_max() -> int:

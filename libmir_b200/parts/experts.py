@@ -1,7 +1,8 @@
 """A mixture of gated experts with a routed choice per token, and an optional shared expert.
 
 With h the feed-forward's input, E experts of which each token uses `top`:
-    s = sigmoid(W_router h)                        32-bit
+    s = sigmoid(W_router h)                        32-bit: the product accumulates and leaves its result in 32-bit (the
+                                                   weights are the stored 16-bit values, h its 16-bit rounding)
     choice = s + correction                        the correction steers the choice only
     a group = E / groups neighbouring experts; its score = the sum of its two largest choice scores; only experts
     of the `keep_groups` best groups can be chosen (the others count as minus infinity)
@@ -34,12 +35,13 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"routed experts: {s.top} of {s.experts} experts cannot be chosen from {s.keep_groups} of "
                              f"{s.groups} groups")
         self.router = self.correction = self.w_gate = self.w_up = self.w_down = None
-        self.shared_gate_up = self.shared_down = self.shared_gate = None
+        self.shared_gate_up = self.shared_down = None
+        self.shared_gate = False
 
     def parameters(self):
         s = self.spec
         matrix = lambda rows, columns: ParamSpec((rows, columns), accept_transposed=False)
-        table = {"router": ParamSpec((s.experts, s.hidden_size), store="float32", accept_transposed=False)}
+        table = {"router": matrix(s.experts, s.hidden_size)}
         if s.correction:
             table["correction"] = ParamSpec((s.experts,), init="zeros", store="float32")
         for expert in range(s.experts):
@@ -51,19 +53,24 @@ class RoutedExperts(FeedForward):
             table["shared.up"] = matrix(s.shared_size, s.hidden_size)
             table["shared.down"] = matrix(s.hidden_size, s.shared_size)
             if s.shared_gate:
-                table["shared.sg"] = ParamSpec((1, s.hidden_size), store="float32", accept_transposed=False)
+                table["shared.sg"] = matrix(1, s.hidden_size)
         return table
 
     def bind(self, tensors):
         s = self.spec
-        self.router = tensors["router"].contiguous()
+        # the router's rows and, behind them, the shared expert's gate row: one product gives every 32-bit logit
+        rows = [tensors["router"]] + ([tensors["shared.sg"].reshape(1, -1)] if s.shared_size and s.shared_gate else [])
+        padding = -(s.experts + len(rows) - 1) % 8
+        if padding:
+            rows.append(torch.zeros((padding, s.hidden_size), dtype=tensors["router"].dtype, device=tensors["router"].device))
+        self.router = torch.cat(rows, dim=0).contiguous()
         self.correction = tensors["correction"].contiguous() if s.correction else None
         stack = lambda name: torch.stack([tensors[f"e{expert}.{name}"] for expert in range(s.experts)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
         if s.shared_size:
             self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0)
             self.shared_down = tensors["shared.down"].contiguous()
-            self.shared_gate = tensors["shared.sg"].reshape(-1).contiguous() if s.shared_gate else None
+            self.shared_gate = bool(s.shared_gate)
 
     def weight_bytes(self):
         """What a step reads at most: the router, the shared expert, and `top` experts per token would be the least; a
@@ -77,8 +84,10 @@ class RoutedExperts(FeedForward):
         dtype = self.env.dtype
         ids = ctx.alloc((tokens, s.top), torch.int32)
         weights = ctx.alloc((tokens, s.top), torch.float32)
-        gate = ctx.alloc((tokens,), torch.float32) if self.shared_gate is not None else None
-        kernels.moe_route(x, self.router, self.correction, self.shared_gate, ids, weights, gate, s.top, s.groups,
+        gate = ctx.alloc((tokens,), torch.float32) if self.shared_gate else None
+        logits = ctx.alloc((tokens, self.router.shape[0]), torch.float32)
+        kernels.linear(x, self.router, logits, alloc=ctx.alloc)       # 32-bit accumulation and result
+        kernels.moe_route(logits, self.correction, self.shared_gate, ids, weights, gate, s.experts, s.top, s.groups,
                           s.keep_groups, s.scale)
         found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size))
         hidden = ctx.alloc((tokens * s.top, s.expert_size), dtype)

@@ -48,8 +48,8 @@ class SwiGlu(FeedForward):
 
 class GeluMlp(FeedForward):
     """down(gelu(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit: the tanh form
-    in the epilogue of the up projection where our own products run it, else on the product's rows, in place; the
-    exact (erf) form always on the product's rows."""
+    or the exact (erf) form, in the epilogue of the up projection where our own products run it, else on the
+    product's rows, in place."""
 
     graph_safe = True
     takes_normed_residual = True
@@ -74,9 +74,6 @@ class GeluMlp(FeedForward):
 
     def forward(self, ctx, x, residual):
         hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)   # (x may be a folded norm)
-        if self.spec.activation == "gelu_erf":
-            kernels.linear(x, self.w_up, hidden, alloc=ctx.alloc)
-            kernels.gelu_erf(hidden)
-        else:
-            kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc)     # the activation in the product's epilogue
+        # the activation in the product's epilogue
+        kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc, exact=self.spec.activation == "gelu_erf")
         ctx.accumulate(hidden, self.w_down, residual)

@@ -107,34 +107,74 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     }
   }
   const size_t head_at = (size_t)head * dim;
-  for (int from = start; from < end; from += kScanChunk) {
+  // What the next chunk needs is fetched into registers before the walk over the current chunk starts and goes to
+  // shared memory after it, so that the walk never waits for global memory.  A warp stages whole tokens: r, k and
+  // the decay exp(-exp(z + w0)) of every channel, and the token's bonus term sum_i r_i u_i k_i, which is the same for
+  // every column of the head.
+  constexpr int TOKENS_PER_WARP = kScanChunk / kScanWarps;
+  constexpr int PER_LANE = PADDED / 32;
+  constexpr int VALUES_PER_THREAD = kScanChunk * BLOCK_COLUMNS / (kScanWarps * 32);
+  float next_r[TOKENS_PER_WARP][PER_LANE], next_k[TOKENS_PER_WARP][PER_LANE], next_w[TOKENS_PER_WARP][PER_LANE];
+  float next_v[VALUES_PER_THREAD];
+  auto fetch = [&](int from) {
     const int count = min(kScanChunk, end - from);
-    __syncthreads();                                             // the chunk before has been read
-    // a warp stages whole tokens: r, k and the decay exp(-exp(z + w0)) of every channel, and the token's bonus term
-    // sum_i r_i u_i k_i, which is the same for every column of the head
-    for (int t = warp; t < count; t += kScanWarps) {
+#pragma unroll
+    for (int tt = 0; tt < TOKENS_PER_WARP; ++tt) {
+      const int t = warp + tt * kScanWarps;
+#pragma unroll
+      for (int e = 0; e < PER_LANE; ++e) {
+        const int i = lane + 32 * e;
+        next_r[tt][e] = 0.0f; next_k[tt][e] = 0.0f; next_w[tt][e] = 0.0f;
+        if (t < count && i < dim) {
+          const size_t source = (size_t)(from + t) * ld + head_at + i;
+          next_r[tt][e] = to_float(r[source]);
+          next_k[tt][e] = to_float(k[source]);
+          next_w[tt][e] = decay_raw[(size_t)(from + t) * width + head_at + i];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VALUES_PER_THREAD; ++j) {
+      const int index = thread + j * kScanWarps * 32;
+      const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
+      next_v[j] = (t < count && first_column + c < dim) ? to_float(v[(size_t)(from + t) * ld + head_at + first_column + c]) : 0.0f;
+    }
+  };
+  auto commit = [&](int from) {
+    const int count = min(kScanChunk, end - from);
+#pragma unroll
+    for (int tt = 0; tt < TOKENS_PER_WARP; ++tt) {
+      const int t = warp + tt * kScanWarps;
+      if (t >= count) continue;                                  // (the same for the whole warp)
       float* at = staged + t * ROW;
       float sum = 0.0f;
-      for (int i = lane; i < PADDED; i += 32) {
-        float rr = 0.0f, kk = 0.0f, ww = 0.0f;
+#pragma unroll
+      for (int e = 0; e < PER_LANE; ++e) {
+        const int i = lane + 32 * e;
+        float ww = 0.0f;
         if (i < dim) {
-          const size_t source = (size_t)(from + t) * ld + head_at + i;
-          rr = to_float(r[source]);
-          kk = to_float(k[source]);
-          ww = expf(-expf(decay_raw[(size_t)(from + t) * width + head_at + i] + decay_bias[head_at + i]));
-          sum = fmaf(rr * bonus[head_at + i], kk, sum);
+          ww = expf(-expf(next_w[tt][e] + decay_bias[head_at + i]));
+          sum = fmaf(next_r[tt][e] * bonus[head_at + i], next_k[tt][e], sum);
         }
-        at[i] = rr; at[PADDED + i] = kk; at[2 * PADDED + i] = ww;
+        at[i] = next_r[tt][e]; at[PADDED + i] = next_k[tt][e]; at[2 * PADDED + i] = ww;
       }
       sum = warp_sum(sum);
       if (lane == 0) at[3 * PADDED] = sum;
     }
-    for (int index = thread; index < count * BLOCK_COLUMNS; index += kScanWarps * 32) {
+#pragma unroll
+    for (int j = 0; j < VALUES_PER_THREAD; ++j) {
+      const int index = thread + j * kScanWarps * 32;
       const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
-      staged[t * ROW + 3 * PADDED + 4 + c] =
-          first_column + c < dim ? to_float(v[(size_t)(from + t) * ld + head_at + first_column + c]) : 0.0f;
+      staged[t * ROW + 3 * PADDED + 4 + c] = next_v[j];
     }
+  };
+  fetch(start);
+  for (int from = start; from < end; from += kScanChunk) {
+    const int count = min(kScanChunk, end - from);
+    __syncthreads();                                             // the chunk before has been read
+    commit(from);
     __syncthreads();
+    if (from + kScanChunk < end) fetch(from + kScanChunk);
     const float* in = staged - ROW;
 #pragma unroll 2
     for (int t = 0; t < count; ++t) {

@@ -66,7 +66,8 @@ _SIGNATURES = {
         "mir_moe_route": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_void_p],
         "mir_moe_tile_slots": [c_int, c_int, c_int],
-        "mir_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "mir_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_void_p],
         "mir_moe_gate_up": [c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_down": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -776,6 +777,7 @@ class ExpertOrder:
         self.offsets = alloc((experts + 1,), torch.int32)
         self.tiles = alloc((2 * slots,), torch.int32)
         self.tile_count = alloc((1,), torch.int32)
+        self.scratch = alloc((2, experts), torch.int32)            # counts and first tiles while sorting
 
 
 EXPERT_TENSOR_CORES = True       # False: the grouped products of routed experts always run as 32-bit multiply-adds
@@ -795,7 +797,8 @@ def moe_sort(ids: torch.Tensor, experts: int, alloc, tile_pairs: int = 8) -> Exp
     found = ExpertOrder(alloc, ids.numel(), experts, tile_pairs)
     lib = library("core")
     _check(lib, lib.mir_moe_sort(ids.data_ptr(), ids.numel(), experts, tile_pairs, found.order.data_ptr(),
-                                 found.offsets.data_ptr(), found.tiles.data_ptr(), found.tile_count.data_ptr(), _stream()))
+                                 found.offsets.data_ptr(), found.tiles.data_ptr(), found.tile_count.data_ptr(),
+                                 found.scratch[0].data_ptr(), found.scratch[1].data_ptr(), _stream()))
     return found
 
 

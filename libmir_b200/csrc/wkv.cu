@@ -58,7 +58,8 @@ __global__ void wkv_tail_kernel(const T* __restrict__ h, long long ld, float* __
 
 constexpr int kScanWarps = 4;
 constexpr int kScanChunkNarrow = 32;                              // tokens staged at a time: heads up to 64 wide,
-constexpr int kScanChunkWide = 16;                                // and wider ones (the stage stays under 48 KB)
+constexpr int kScanChunkWide = 16;                                // up to 128 wide,
+constexpr int kScanChunkWidest = 8;                               // and wider ones (the stage stays under 48 KB)
 constexpr int kLanes = 8;                                        // lanes that share one column of the state
 
 // blockDim (32, kScanWarps), grid (rows, heads, ceil(dim / (kScanWarps * 4))).  Lane l of a column holds the key
@@ -75,7 +76,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   constexpr int BLOCK_COLUMNS = COLUMNS * kScanWarps;
   constexpr int PADDED = kLanes * PER;
   constexpr int ROW = 3 * PADDED + 4 + BLOCK_COLUMNS;            // r | k | decay | bonus term | v of this CTA's columns
-  constexpr int kScanChunk = PER <= 8 ? kScanChunkNarrow : kScanChunkWide;
+  constexpr int kScanChunk = PER <= 8 ? kScanChunkNarrow : (PER <= 16 ? kScanChunkWide : kScanChunkWidest);
   __shared__ __align__(16) float staged[kScanChunk * ROW];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -239,8 +240,10 @@ int launch_scan_for(cudaStream_t stream, const void* r, const void* k, const voi
   if (dim <= 64) { MIR_WKV(8) }
   if (dim <= 96) { MIR_WKV(12) }
   if (dim <= 128) { MIR_WKV(16) }
+  if (dim <= 192) { MIR_WKV(24) }
+  if (dim <= 256) { MIR_WKV(32) }
 #undef MIR_WKV
-  mir_set_error("wkv_scan: heads of %d channels are wider than 128", dim);
+  mir_set_error("wkv_scan: heads of %d channels are wider than 256", dim);
   return MIR_BAD_ARGUMENT;
 }
 

@@ -37,8 +37,8 @@ class Wkv(Mixer):
         s = spec
         if min(s.heads, s.head_dim, s.decay_rank) <= 0:
             raise ValueError("wkv needs heads, head_dim and decay_rank above zero")
-        if s.head_dim > 128:
-            raise ValueError("the recurrence kernel takes heads up to 128 wide")
+        if s.head_dim > 256:
+            raise ValueError("the recurrence kernel takes heads up to 256 wide")
         self.width = s.heads * s.head_dim
         self.mu = self.w_r = self.w_k = self.w_v = self.w_g = self.w_1 = self.w_2 = self.w_o = None
         self.decay_bias = self.bonus = self.norm = None

@@ -310,7 +310,7 @@ def test_kernels_refuse_sizes_they_do_not_take():
                                         torch.zeros(4, 1, 648, device="cuda"),
                                         torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
                                         torch.zeros(1, dtype=torch.int32, device="cuda"),
-                                        torch.zeros(1, dtype=torch.int32, device="cuda"), 4, 1, 1, 520, 1.0, None)
+                                        torch.zeros(1, dtype=torch.int32, device="cuda"), 4, 1, 1, 648, 1.0, None)
     with pytest.raises(KernelError, match="CUDA tensors only"):
         kernels.silu_mul(torch.zeros(1, 4), torch.zeros(1, 2))
     with pytest.raises(KernelError, match="shapes or strides"):

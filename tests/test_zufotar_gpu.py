@@ -344,7 +344,7 @@ def plain_wkv_recurrence(r, k, v, decay, bonus, state):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim", [(2, 64), (3, 20), (1, 128), (4, 6), (2, 100), (5, 32)])
+@pytest.mark.parametrize("heads,dim", [(2, 64), (3, 20), (1, 128), (4, 6), (2, 100), (5, 32), (1, 160), (2, 256)])
 def test_wkv_recurrence_against_the_plain_one(dtype, heads, dim):
     """The recurrence in portions with carried state, several requests in one launch (single tokens beside portions),
     other slots untouched; the inputs are the kernel's own (rounded) inputs, so the comparison is 32-bit sharp."""

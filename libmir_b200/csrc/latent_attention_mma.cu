@@ -142,7 +142,8 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         for (int e = 0; e < 4; ++e) s[mt][e] = 0.0f;
       const __nv_bfloat16* b_at = k_s + (size_t)(warp * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8;
       const __nv_bfloat16* a_at = q_s + (size_t)(lane & 15) * ld + (lane >> 4) * 8;
-      for (int k = 0; k < padded; k += 16) {
+#pragma unroll 4
+      for (int k = 0; k < padded; k += 16) {                      // (unrolled: the loads of later steps start early)
         unsigned b[2];
         ldmatrix_x2(b, b_at + k);
 #pragma unroll

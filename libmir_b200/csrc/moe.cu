@@ -332,9 +332,9 @@ __device__ __forceinline__ void mma_copy16(void* dst, const void* src) {
 
 // grid (tile slots, ceil(N / TILE_N)), 32 * WARPS_M * WARPS_N threads.  A CTA takes up to TILE_M sorted pairs of one
 // expert and TILE_N outputs (GATED: TILE_N gate rows and the TILE_N up rows beside them); its warps form a WARPS_M x
-// WARPS_N grid over the tile.  One shape is built: 64 x 64 with 4 x 1 warps (128 x 128 with 2 x 4 warps of 64 x 32
-// each was measured too: 752 against 552 us for the gate and up products of 12,288 pairs over 64 experts, where an
-// expert's 192 pairs fill one and a half such tiles).  K is a multiple of 8.  Rows and results as in moe_grouped_kernel.  Dynamic shared memory:
+// WARPS_N grid over the tile.  One shape is built: 64 x 64 with 2 x 2 warps of 32 x 32 (128 x 128 with 2 x 4 warps of
+// 64 x 32 each was measured too: 752 against 552 us for the gate and up products of 12,288 pairs over 64 experts,
+// where an expert's 192 pairs fill one and a half such tiles).  K is a multiple of 8.  Rows and results as in moe_grouped_kernel.  Dynamic shared memory:
 // kMmaStages x (TILE_M + weight rows) x kMmaLd bf16, then TILE_M ints.
 template <bool GATED, typename TO, int TILE_M, int TILE_N, int WARPS_M, int WARPS_N>
 __global__ void __launch_bounds__(32 * WARPS_M * WARPS_N)
@@ -477,7 +477,7 @@ int launch_grouped_mma(cudaStream_t stream, int tile_pairs, const void* x, long 
                        int gather_div, const void* w_a, const void* w_b, void* out, long long ldo, const int* scatter,
                        const int* tiles, const int* tile_count, const int* offsets, int pairs, int experts, int K, int N) {
   (void)tile_pairs;
-  return launch_grouped_mma_as<GATED, TO, 64, 64, 4, 1>(stream, x, ldx, gather, gather_div, w_a, w_b, out, ldo, scatter,
+  return launch_grouped_mma_as<GATED, TO, 64, 64, 2, 2>(stream, x, ldx, gather, gather_div, w_a, w_b, out, ldo, scatter,
                                                         tiles, tile_count, offsets, pairs, experts, K, N);
 }
 

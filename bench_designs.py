@@ -187,17 +187,17 @@ def zufotar_kernel_table(s, tools) -> dict:
         calls = [lambda: kernels.moe_route(logits, correction, True, ids, weights, shared_gate, experts, top,
                                            s["groups"][0], s["groups"][1], 2.5)]
         table[f"{label}_moe_route"] = timed(calls, tokens * (experts + 8) * 4, hbm)
-        tile = kernels.expert_tile_pairs(bf16, width, ff)
+        tile = kernels.expert_tile_pairs(bf16, width, ff, pairs, experts)
         found = kernels.moe_sort(ids, experts, alloc, tile)
         table[f"{label}_moe_sort"] = timed([lambda: kernels.moe_sort(ids, experts, alloc, tile)], pairs * 8, hbm)
         torch.cuda.synchronize()
         used = int(torch.unique(ids).numel())
         banks = max(2, min(8, -(-(300 << 20) // (experts * ff * width * 6))))
-        gates = [rand(experts, ff, width, scale=0.03) for _ in range(banks)]
-        ups = [rand(experts, ff, width, scale=0.03) for _ in range(banks)]
+        both = [rand(2 * experts, ff, width, scale=0.03) for _ in range(banks)]        # gate rows, the up rows behind them
+        gates, ups = [b[:experts] for b in both], [b[experts:] for b in both]
         downs = [rand(experts, width, ff, scale=0.03) for _ in range(banks)]
         hidden = torch.empty(pairs, ff, device=device, dtype=bf16)
-        calls = [lambda g=g, u=u: kernels.moe_gate_up(h, found, top, g, u, hidden) for g, u in zip(gates, ups)]
+        calls = [lambda g=g, u=u: kernels.moe_gate_up(h, found, top, g, u, hidden, alloc) for g, u in zip(gates, ups)]
         table[f"{label}_moe_gate_up"] = timed(calls, 4.0 * pairs * ff * width, flops_peak) if prompt else \
             timed(calls, used * 2 * ff * width * 2, hbm)
         pair_rows = torch.empty(pairs, width, device=device, dtype=f32)

@@ -56,6 +56,19 @@ enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3, GELU = 4, GELU_
 
 __device__ int g_tc_gemm_error = 0;
 
+// The rows of a grouped product (routed experts): the rows are sorted by group, every group multiplies with its own
+// weight rows, and which tiles of 128 rows there are is known on the device only.  tiles[2 i], tiles[2 i + 1]: group and
+// first row of tile i (a tile ends with its group's rows, offsets[group + 1], the rest of its 128 rows is computed and
+// dropped); tile_count[0] tiles in all; group g's weight rows start at row g * group_rows of the weight matrix; the
+// result of sorted row r goes to row scatter[r] of out (to row r without scatter).  tiles == nullptr: a plain product.
+struct GroupedRows {
+  const int* tiles;
+  const int* tile_count;
+  const int* offsets;
+  const int* scatter;
+  int group_rows;
+};
+
 // One CTA per SM walks over output tiles (token tile fastest, so CTAs that run together share weight rows in
 // L2).  A tile is 128 tokens x `width` accumulator columns (width a multiple of 16, at most 256; with the SwiGLU
 // epilogue width / 2 gate columns followed by width / 2 up columns).  Two accumulators of 256 columns alternate,
@@ -64,7 +77,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
-               int width, int token_tiles, int tiles) {
+               int width, int token_tiles, int tiles, GroupedRows grouped, int column_tiles) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[2 * kStages + 4];   // full, empty, accumulator full[2], free[2]
   __shared__ uint32_t tmem_base_slot;
@@ -101,6 +114,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
   const uint32_t tmem_base = tmem_base_slot;
   grid_launch_dependents();
   grid_dependency_wait();                                   // x (and out for ACCUM) come from earlier kernels
+  if (grouped.tiles != nullptr) {                           // the list of row tiles was written by an earlier kernel
+    token_tiles = grouped.tile_count[0];
+    tiles = token_tiles * column_tiles;
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -109,7 +126,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
       uint32_t count = 0;                                    // stages filled so far, over all tiles
       bool alive = true;
       for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-        const int m0 = (tile % token_tiles) * kTileM, n0 = (tile / token_tiles) * out_width;
+        const int row_tile = tile % token_tiles, n0 = (tile / token_tiles) * out_width;
+        const int m0 = grouped.tiles != nullptr ? grouped.tiles[2 * row_tile + 1] : row_tile * kTileM;
+        const int w0 = n0 + (grouped.tiles != nullptr ? grouped.tiles[2 * row_tile] * grouped.group_rows : 0);
         for (int step = 0; step < steps; ++step, ++count) {
           const uint32_t stage = count % kStages, parity = (count / kStages) & 1u;
           if (!wait_barrier(empty0 + 8 * stage, parity ^ 1u)) { g_tc_gemm_error = 1; alive = false; break; }
@@ -123,12 +142,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
           // the weight map's box has out_width rows: one box, or a gate box and an up box behind it
           asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-                  "r"(dst + kTileM * 128), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(n0)
+                  "r"(dst + kTileM * 128), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(w0)
               : "memory");
           if (MODE == SWIGLU)
             asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-                    "r"(dst + (kTileM + out_width) * 128), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(up_offset + n0)
+                    "r"(dst + (kTileM + out_width) * 128), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(up_offset + w0)
                 : "memory");
         }
       }
@@ -172,8 +191,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
     bool alive = true;
     for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++local) {
       const uint32_t buffer = local & 1u, use = (local >> 1) & 1u;
-      const int m0 = (tile % token_tiles) * kTileM, n0 = (tile / token_tiles) * out_width;
-      const int row = m0 + quarter * 32 + lane;
+      const int row_tile = tile % token_tiles, n0 = (tile / token_tiles) * out_width;
+      const int m0 = grouped.tiles != nullptr ? grouped.tiles[2 * row_tile + 1] : row_tile * kTileM;
+      const int row_end = grouped.tiles != nullptr ? grouped.offsets[grouped.tiles[2 * row_tile] + 1] : m;
+      const int source_row = m0 + quarter * 32 + lane;
+      // where this thread's row of results goes: its own row, or the place the sorted row came from
+      const int row = (grouped.tiles != nullptr && grouped.scatter != nullptr && source_row < row_end)
+                          ? grouped.scatter[source_row] : source_row;
       if (!wait_barrier(acc_full0 + 8 * buffer, use)) { g_tc_gemm_error = 3; alive = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t lane_base = tmem_base + buffer * 256u + ((uint32_t)(quarter * 32) << 16);
@@ -208,7 +232,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
         }
         if (c0 + 64 >= out_width) release();                 // the last columns are in registers
         const int limit = min(n, n0 + out_width);            // columns of this tile that exist
-        if (row < m) {
+        if (source_row < row_end) {
           if (MODE == STORE || MODE == SWIGLU || MODE == GELU || MODE == GELU_ERF) {
             bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + n0 + c0;
             if (n0 + c0 + 32 <= limit && (ldo % 8) == 0) {
@@ -320,7 +344,37 @@ int launch(const void* x, int ldx, const void* w, const void* bias, void* out, i
   if (tiles > 0x7fffffffll) { mir_set_error("tc_gemm: too many tiles"); return MIR_BAD_ARGUMENT; }
   const dim3 grid((unsigned)std::min<long long>(tiles, sm_count()));
   return mir_launch("tc_gemm", tc_gemm_kernel<MODE>, grid, dim3(kThreads), smem, stream, 0, x_map, w_map, bias, out, ldo,
-                    m, n, k, up_offset, width, token_tiles, (int)tiles);
+                    m, n, k, up_offset, width, token_tiles, (int)tiles, GroupedRows{nullptr, nullptr, nullptr, nullptr, 0}, 0);
+}
+
+// The grouped form: x [rows, k] sorted by group, w [weight_rows, k] with group g's n rows from row g * n on (and, for
+// the SwiGLU epilogue, its up rows up_offset further), the row tiles from a list on the device (at most max_row_tiles).
+template <int MODE>
+int launch_grouped(const void* x, int ldx, int rows, const void* w, int weight_rows, void* out, int ldo, int n, int k,
+                   int up_offset, const GroupedRows& grouped, int max_row_tiles, cudaStream_t stream) {
+  const int width = MODE == SWIGLU ? choose_width(2ll * n, 32) : choose_width(n, 16);
+  const int out_width = MODE == SWIGLU ? width / 2 : width;
+  CUtensorMap x_map, w_map;
+  int status = tensor_map_for(x, rows, k, ldx, kTileM, &x_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(w, weight_rows, k, k, out_width, &w_map);
+  if (status != MIR_OK) return status;
+  const size_t smem = (size_t)kStages * kStageStride + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err = cudaFuncSetAttribute(tc_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+      mir_set_error("tc_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+      return MIR_CUDA_ERROR;
+    }
+    configured = true;
+  }
+  const int column_tiles = (n + out_width - 1) / out_width;
+  const long long tiles = (long long)column_tiles * max_row_tiles;
+  if (tiles > 0x7fffffffll) { mir_set_error("tc_gemm: too many tiles"); return MIR_BAD_ARGUMENT; }
+  const dim3 grid((unsigned)std::min<long long>(std::max<long long>(tiles, 1), sm_count()));
+  return mir_launch("tc_gemm_grouped", tc_gemm_kernel<MODE>, grid, dim3(kThreads), smem, stream, 0, x_map, w_map,
+                    (const void*)nullptr, out, ldo, rows, n, k, up_offset, width, 0, 0, grouped, column_tiles);
 }
 
 }  // namespace
@@ -331,6 +385,31 @@ MIR_EXPORT int mir_gemm_tc_error() {
   int flag = 0;
   if (cudaMemcpyFromSymbol(&flag, g_tc_gemm_error, sizeof(int)) != cudaSuccess) return -1;
   return flag;
+}
+
+// The products of routed experts on rows sorted by expert.  mode 3 (SwiGLU): out bf16 [rows, n] = silu(x w_gate[g]^T) *
+// (x w_up[g]^T) with w = [experts * n gate rows; experts * n up rows] (up_offset = experts * n); mode 2: out float
+// [*, n] = x w[g]^T, the row of sorted row r written to out row scatter[r].  tiles / tile_count / offsets: the list of
+// 128-row tiles, their number and the experts' row ranges, all on the device; max_row_tiles bounds the list.  k and ldx
+// multiples of 8, x and w 16-byte aligned.
+MIR_EXPORT int mir_gemm_tc_grouped_bf16(int mode, const void* x, int ldx, int rows, const void* w, int experts,
+                                        void* out, int ldo, int n, int k, const int* tiles, const int* tile_count,
+                                        const int* offsets, const int* scatter, int max_row_tiles, cudaStream_t stream) {
+  if (rows == 0 || n == 0) return MIR_OK;
+  if (rows < 0 || n < 0 || k <= 0 || (k % 8) || (ldx % 8) || ldx < k || ldo < n || ((uintptr_t)x & 15) ||
+      ((uintptr_t)w & 15) || experts <= 0 || max_row_tiles <= 0 || tiles == nullptr || tile_count == nullptr ||
+      offsets == nullptr) {
+    mir_set_error("tc_gemm_grouped: k and the row stride must be multiples of 8 and the operands 16-byte aligned "
+                  "(rows %d n %d k %d ldx %d ldo %d)", rows, n, k, ldx, ldo);
+    return MIR_BAD_ARGUMENT;
+  }
+  const GroupedRows grouped{tiles, tile_count, offsets, scatter, n};
+  if (mode == SWIGLU)
+    return launch_grouped<SWIGLU>(x, ldx, rows, w, 2 * experts * n, out, ldo, n, k, experts * n, grouped, max_row_tiles, stream);
+  if (mode == F32)
+    return launch_grouped<F32>(x, ldx, rows, w, experts * n, out, ldo, n, k, 0, grouped, max_row_tiles, stream);
+  mir_set_error("tc_gemm_grouped: mode %d is neither the SwiGLU nor the float epilogue", mode);
+  return MIR_BAD_ARGUMENT;
 }
 
 // For measurements: fix the accumulator width of a tile (a multiple of 32, 32..256), or 0 to let the launcher

@@ -307,6 +307,7 @@ moe_grouped_kernel(const T* __restrict__ x, long long ldx, const int* __restrict
 
 // ---- the grouped products on tensor cores (bf16) -------------------------------------------------------------------
 constexpr int kMmaTile = 64;          // pairs of one expert per CTA
+constexpr int kTensorTile = 128;      // rows of a tile of the tcgen05 grouped product (csrc/gemm_tc.cu)
 constexpr int kMmaStep = 32;          // inputs per stage
 constexpr int kMmaLd = kMmaStep + 8;  // row stride in shared memory: 80 bytes, so that ldmatrix meets no bank twice
 constexpr int kMmaStages = 3;         // a ring of three stages: two loads are in flight while one is multiplied
@@ -535,13 +536,13 @@ MIR_EXPORT int mir_moe_route(const float* logits, long long ld, const float* cor
 // ints for each).
 MIR_EXPORT int mir_moe_tile_slots(int pairs, int experts, int tile_pairs) { return pairs / tile_pairs + experts; }
 
-// tile_pairs: 8 for the 32-bit grouped products, 64 for the tensor-core ones.
+// tile_pairs: 8 for the 32-bit grouped products, 64 for the mma.sync ones, 128 for the tcgen05 ones.
 // counts, first_tile: scratch of `experts` ints each.
 MIR_EXPORT int mir_moe_sort(const int* ids, int pairs, int experts, int tile_pairs, int* order, int* offsets, int* tiles,
                             int* tile_count, int* counts, int* first_tile, cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
   if (pairs < 0 || experts <= 0 || experts > kMaxExperts ||
-      (tile_pairs != kExpertTile && tile_pairs != kMmaTile)) {
+      (tile_pairs != kExpertTile && tile_pairs != kMmaTile && tile_pairs != kTensorTile)) {
     mir_set_error("moe_sort: bad sizes (pairs %d, experts %d, tiles of %d)", pairs, experts, tile_pairs);
     return MIR_BAD_ARGUMENT;
   }
@@ -590,6 +591,32 @@ MIR_EXPORT int mir_moe_down(int bf16, const void* hidden, const int* order, cons
                                                        width);
   return launch_grouped<float, float, false>(stream, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows, width, order,
                                              tiles, tile_count, offsets, pairs, experts, inter, width);
+}
+
+// sorted[i, :] = h[order[i] / top, :]: the tokens' rows in the order of the sorted pairs (16-byte pieces).
+__global__ void moe_gather_rows_kernel(const uint4* __restrict__ h, long long ld_pieces, const int* __restrict__ order, int top,
+                                       uint4* __restrict__ sorted, int pieces, size_t total) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const size_t row = index / pieces;
+  const int piece = (int)(index - row * pieces);
+  sorted[index] = h[(size_t)(order[row] / top) * ld_pieces + piece];
+}
+
+// h [tokens, width] bfloat16 (row stride ld, both multiples of 8); sorted [pairs, width].
+MIR_EXPORT int mir_moe_gather_rows(const void* h, long long ld, const int* order, int top, void* sorted, int pairs,
+                                   int width, cudaStream_t stream) {
+  if (pairs == 0) return MIR_OK;
+  if (pairs < 0 || width <= 0 || width % 8 || ld % 8 || top <= 0) {
+    mir_set_error("moe_gather_rows: rows of 16-byte pieces are needed (width %d, stride %lld)", width, ld);
+    return MIR_BAD_ARGUMENT;
+  }
+  const int pieces = width / 8;
+  const size_t total = (size_t)pairs * pieces;
+  return mir_launch("moe_gather_rows", moe_gather_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 0,
+                    (const uint4*)h, ld / 8, order, top, (uint4*)sorted, pieces, total);
 }
 
 MIR_EXPORT int mir_moe_combine(float* residual, const float* pair_rows, const float* weights, const float* shared_rows,

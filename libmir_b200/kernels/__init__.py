@@ -72,6 +72,7 @@ _SIGNATURES = {
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_down": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_int, c_int, c_void_p],
+        "mir_moe_gather_rows": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "mir_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
@@ -119,6 +120,8 @@ _SIGNATURES = {
         "mir_gemm_tc_stream_set_splits": [c_int, c_int, c_int],
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
+        "mir_gemm_tc_grouped_bf16": [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_set_width": [c_int],
         "mir_gemm_tc_error": [],
         "mir_linear_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -783,15 +786,23 @@ class ExpertOrder:
 EXPERT_TENSOR_CORES = True       # False: the grouped products of routed experts always run as 32-bit multiply-adds
 
 
-def expert_tile_pairs(dtype: torch.dtype, width: int, inter: int) -> int:
-    """The tile the grouped products of routed experts work on: 64 pairs on tensor cores (bfloat16 rows of 16-byte
-    pieces), else 8 pairs with 32-bit multiply-adds."""
-    return 64 if (EXPERT_TENSOR_CORES and dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0) else 8
+EXPERT_TCGEN05_MIN_PAIRS = 48    # pairs per expert (on average) from which the grouped products run on tcgen05
+
+
+def expert_tile_pairs(dtype: torch.dtype, width: int, inter: int, pairs: int = 0, experts: int = 1) -> int:
+    """The tile the grouped products of routed experts work on.  bfloat16 rows of 16-byte pieces run on tensor cores:
+    tiles of 128 pairs through the tcgen05 product (TMA, accumulators in tensor memory) where an expert gets
+    EXPERT_TCGEN05_MIN_PAIRS pairs or more on average, else tiles of 64 pairs through the mma.sync kernel that streams
+    each expert's weights once; everything else runs tiles of 8 pairs with 32-bit multiply-adds."""
+    if not (EXPERT_TENSOR_CORES and dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0):
+        return 8
+    many = EXPERT_TCGEN05_MIN_PAIRS > 0 and pairs >= max(128, EXPERT_TCGEN05_MIN_PAIRS * max(1, experts))
+    return 128 if many else 64
 
 
 def moe_sort(ids: torch.Tensor, experts: int, alloc, tile_pairs: int = 8) -> ExpertOrder:
     """Order the pairs of ids [tokens, top] by expert (a pair's place among its expert's pairs follows its index) and
-    cut each expert's run into tiles of tile_pairs (8 or 64) pairs."""
+    cut each expert's run into tiles of tile_pairs (8, 64 or 128) pairs."""
     _cuda(ids)
     _require(ids.dtype == torch.int32 and ids.is_contiguous(), "moe_sort: contiguous int32 ids are needed")
     found = ExpertOrder(alloc, ids.numel(), experts, tile_pairs)
@@ -803,9 +814,11 @@ def moe_sort(ids: torch.Tensor, experts: int, alloc, tile_pairs: int = 8) -> Exp
 
 
 def moe_gate_up(h: torch.Tensor, found: ExpertOrder, top: int, w_gate: torch.Tensor, w_up: torch.Tensor,
-                hidden: torch.Tensor) -> None:
+                hidden: torch.Tensor, alloc=None) -> None:
     """hidden[i] = silu(w_gate[e] x) * (w_up[e] x) for the i-th pair in expert order, x its token's row of h and e its
-    expert; w_gate, w_up [experts, inter, width]; hidden [pairs, inter]."""
+    expert; w_gate, w_up [experts, inter, width]; hidden [pairs, inter].  With tiles of 128 pairs (the tcgen05 product)
+    the tokens' rows are first brought into the pairs' order (scratch from `alloc`), and w_up must lie right behind
+    w_gate in memory (the two halves of one tensor)."""
     _cuda(h, w_gate, w_up, hidden)
     tokens, width = h.shape
     experts, inter = w_gate.shape[0], w_gate.shape[1]
@@ -813,6 +826,20 @@ def moe_gate_up(h: torch.Tensor, found: ExpertOrder, top: int, w_gate: torch.Ten
              and w_gate.is_contiguous() and w_up.is_contiguous() and hidden.is_contiguous()
              and hidden.shape == (found.pairs, inter) and found.pairs == tokens * top and found.experts == experts
              and h.dtype == w_gate.dtype == w_up.dtype == hidden.dtype, "moe_gate_up: shapes or dtypes do not fit")
+    if found.tile_pairs == 128:
+        _require(h.dtype == torch.bfloat16 and alloc is not None
+                 and w_up.data_ptr() == w_gate.data_ptr() + w_gate.numel() * 2,
+                 "moe_gate_up: the tcgen05 product takes bfloat16, scratch memory and w_up right behind w_gate")
+        ordered = alloc((found.pairs, width), torch.bfloat16)
+        core = library("core")
+        _check(core, core.mir_moe_gather_rows(h.data_ptr(), h.stride(0), found.order.data_ptr(), top, ordered.data_ptr(),
+                                              found.pairs, width, _stream()))
+        lib = library("bf16")
+        _check(lib, lib.mir_gemm_tc_grouped_bf16(MODE_SWIGLU, ordered.data_ptr(), width, found.pairs, w_gate.data_ptr(),
+                                                 experts, hidden.data_ptr(), inter, inter, width, found.tiles.data_ptr(),
+                                                 found.tile_count.data_ptr(), found.offsets.data_ptr(), None,
+                                                 found.pairs // 128 + experts, _stream()))
+        return
     lib = library("core")
     _check(lib, lib.mir_moe_gate_up(_is_bf16(h), h.data_ptr(), h.stride(0), found.order.data_ptr(), top,
                                     w_gate.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), found.tiles.data_ptr(),
@@ -828,6 +855,14 @@ def moe_down(hidden: torch.Tensor, found: ExpertOrder, w_down: torch.Tensor, pai
              and hidden.dtype == w_down.dtype and pair_rows.dtype == torch.float32 and pair_rows.is_contiguous()
              and pair_rows.shape == (found.pairs, width) and found.experts == experts,
              "moe_down: shapes or dtypes do not fit")
+    if found.tile_pairs == 128:
+        _require(hidden.dtype == torch.bfloat16, "moe_down: the tcgen05 product takes bfloat16")
+        lib = library("bf16")
+        _check(lib, lib.mir_gemm_tc_grouped_bf16(MODE_F32, hidden.data_ptr(), inter, found.pairs, w_down.data_ptr(), experts,
+                                                 pair_rows.data_ptr(), width, width, inter, found.tiles.data_ptr(),
+                                                 found.tile_count.data_ptr(), found.offsets.data_ptr(),
+                                                 found.order.data_ptr(), found.pairs // 128 + experts, _stream()))
+        return
     lib = library("core")
     _check(lib, lib.mir_moe_down(_is_bf16(hidden), hidden.data_ptr(), found.order.data_ptr(), w_down.data_ptr(),
                                  pair_rows.data_ptr(), found.tiles.data_ptr(), found.tile_count.data_ptr(),

@@ -10,8 +10,9 @@ With h the feed-forward's input, E experts of which each token uses `top`:
     out = sum over chosen of weight * expert(h)    expert(h) = W_down (silu(W_gate h) * (W_up h))
         + sigmoid(w_sg . h) * shared(h)            one number per token gates the shared expert, if there is one
 Everything runs on the device without a count ever being read back (csrc/moe.cu): the (token, expert) pairs are
-ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights (on tensor
-cores in bfloat16, as 32-bit multiply-adds in float32), and one kernel adds the weighted rows, and the shared
+ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights (in bfloat16 on
+tensor cores: the tcgen05 product of csrc/gemm_tc.cu on tiles from a list on the device where experts get many pairs,
+an mma.sync kernel that streams each expert's weights once where they get few; in float32 as 32-bit multiply-adds), and one kernel adds the weighted rows, and the shared
 expert's, into the 32-bit residual.
 """
 
@@ -66,7 +67,10 @@ class RoutedExperts(FeedForward):
         self.router = torch.cat(rows, dim=0).contiguous()
         self.correction = tensors["correction"].contiguous() if s.correction else None
         stack = lambda name: torch.stack([tensors[f"e{expert}.{name}"] for expert in range(s.experts)]).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        # gate and up rows of all experts in one tensor, the up rows behind the gate rows: the tcgen05 grouped product
+        # reads an expert's two slices through one tensor map
+        gate_up = torch.cat([stack("gate"), stack("up")], dim=0).contiguous()
+        self.w_gate, self.w_up, self.w_down = gate_up[:s.experts], gate_up[s.experts:], stack("down")
         if s.shared_size:
             self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0)
             self.shared_down = tensors["shared.down"].contiguous()
@@ -89,9 +93,10 @@ class RoutedExperts(FeedForward):
         kernels.linear(x, self.router, logits, alloc=ctx.alloc)       # 32-bit accumulation and result
         kernels.moe_route(logits, self.correction, self.shared_gate, ids, weights, gate, s.experts, s.top, s.groups,
                           s.keep_groups, s.scale)
-        found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size))
+        found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size, tokens * s.top,
+                                                                                    s.experts))
         hidden = ctx.alloc((tokens * s.top, s.expert_size), dtype)
-        kernels.moe_gate_up(x, found, s.top, self.w_gate, self.w_up, hidden)
+        kernels.moe_gate_up(x, found, s.top, self.w_gate, self.w_up, hidden, ctx.alloc)
         pair_rows = ctx.alloc((tokens * s.top, s.hidden_size), torch.float32)
         kernels.moe_down(hidden, found, self.w_down, pair_rows)
         shared_rows = None

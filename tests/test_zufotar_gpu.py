@@ -433,7 +433,8 @@ def test_router_against_the_plain_one(dtype, experts, top, groups, keep):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("tokens,experts,top,width,inter", [(1, 4, 2, 32, 16), (7, 3, 3, 52, 20), (100, 16, 4, 64, 40),
-                                                            (33, 5, 1, 600, 24), (9, 40, 2, 24, 7), (300, 3, 2, 72, 136)])
+                                                            (33, 5, 1, 600, 24), (9, 40, 2, 24, 7), (300, 3, 2, 72, 136),
+                                                            (700, 5, 3, 264, 200)])
 def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, experts, top, width, inter):
     """Sorting by expert, the two grouped products (32-bit multiply-adds on tiles of 8 pairs, or tensor cores on
     tiles of 64 where the sizes allow) and the weighted sum: experts without any token, experts with more pairs than
@@ -441,15 +442,17 @@ def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, exp
     from libmir_b200 import kernels
     generator = torch.Generator().manual_seed(10)
     h = torch.randn(tokens, width, generator=generator).to(dtype)
-    w_gate, w_up = ((torch.randn(experts, inter, width, generator=generator) * 0.2).to(dtype) for _ in range(2))
+    both = (torch.randn(2 * experts, inter, width, generator=generator) * 0.2).to(dtype)
+    w_gate, w_up = both[:experts], both[experts:]
     w_down = (torch.randn(experts, width, inter, generator=generator) * 0.2).to(dtype)
     ids = torch.stack([torch.randperm(experts, generator=generator)[:top] for _ in range(tokens)]).to(torch.int32)
     if top == 1 and experts > 2:
         ids[ids == 1] = 0                                                    # expert 1 gets no token
     weights = torch.rand(tokens, top, generator=generator)
     alloc = lambda shape, kind: torch.empty(shape, dtype=kind, device=device())
-    tile = kernels.expert_tile_pairs(dtype, width, inter)
-    assert tile == (64 if dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0 else 8)
+    tile = kernels.expert_tile_pairs(dtype, width, inter, tokens * top, experts)
+    on_tensor_cores = dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0
+    assert tile == ((128 if tokens * top >= max(128, 48 * experts) else 64) if on_tensor_cores else 8)
     found = kernels.moe_sort(on_device(ids), experts, alloc, tile)
     order, offsets = found.order.cpu().tolist(), found.offsets.cpu().tolist()
     flat = ids.reshape(-1).tolist()
@@ -466,7 +469,8 @@ def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, exp
         assert offsets[expert] <= start < offsets[expert + 1]
     assert sorted(covered) == list(range(tokens * top))
     hidden = torch.empty(tokens * top, inter, dtype=dtype, device=device())
-    kernels.moe_gate_up(on_device(h), found, top, on_device(w_gate), on_device(w_up), hidden)
+    both = on_device(both)
+    kernels.moe_gate_up(on_device(h), found, top, both[:experts], both[experts:], hidden, alloc)
     pair_rows = torch.empty(tokens * top, width, device=device())
     kernels.moe_down(hidden, found, on_device(w_down), pair_rows)
     shared = torch.randn(tokens, width, generator=generator)
@@ -486,6 +490,8 @@ def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, exp
         kernels.moe_combine(residual, pair_rows, on_device(weights), on_device(rows) if rows is not None else None,
                             on_device(gates) if gates is not None else None)
         close(residual, base.double() + want + extra, tol, f"{tokens} tokens, {experts} experts, top {top}")
+    if dtype == torch.bfloat16:
+        assert kernels.tensor_core_linear_error() == 0
 
 
 # ------------------------------------------------------------------------------ whole models through the engine

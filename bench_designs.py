@@ -187,7 +187,7 @@ def zufotar_kernel_table(s, tools) -> dict:
         calls = [lambda: kernels.moe_route(logits, correction, True, ids, weights, shared_gate, experts, top,
                                            s["groups"][0], s["groups"][1], 2.5)]
         table[f"{label}_moe_route"] = timed(calls, tokens * (experts + 8) * 4, hbm)
-        tile = kernels.expert_tile_pairs(bf16, width, ff, pairs, experts)
+        tile = kernels.expert_tile_pairs(bf16, width, ff)
         found = kernels.moe_sort(ids, experts, alloc, tile)
         table[f"{label}_moe_sort"] = timed([lambda: kernels.moe_sort(ids, experts, alloc, tile)], pairs * 8, hbm)
         torch.cuda.synchronize()

@@ -4,12 +4,13 @@
 //                 the experts of the best groups by score + correction, weights = chosen scores / their sum * scale;
 //                 and the shared expert's gate
 //   moe_sort      the pairs ordered by expert (a stable counting sort: a CTA per expert counts, one CTA scans, a CTA
-//                 per expert places), each expert's range, and the list of tiles (8 or 64 pairs of one expert)
+//                 per expert places), each expert's range, and the list of tiles (8 or 128 pairs of one expert)
 //                 that the grouped products walk over
 //   moe_grouped   products on the sorted pairs with each pair's own expert's weights: hidden = silu(Wg x) * (Wu x)
-//                 from the tokens' rows, and the down projection of the hidden rows into one 32-bit row per pair;
-//                 32-bit multiply-adds on tiles of 8 pairs (any type and size), or bf16 tensor cores (mma.sync
-//                 m16n8k16) on tiles of 64 pairs x 64 outputs with the weights streamed through a cp.async ring
+//                 from the tokens' rows, and the down projection of the hidden rows into one 32-bit row per pair, as
+//                 32-bit multiply-adds on tiles of 8 pairs (any type and size).  bfloat16 rows of 16-byte pieces run
+//                 the tcgen05 product of csrc/gemm_tc.cu instead, on tiles of 128 pairs of this file's list, after
+//                 moe_gather_rows has brought the tokens' rows into the pairs' order
 //   moe_combine   residual[t] += sum over slots of weight * the pair's row (+ gate * the shared expert's row)
 // Everything the host needs to launch them is known before the step: no count is read back.
 #include <cfloat>
@@ -20,6 +21,7 @@ using namespace mir;
 namespace {
 
 constexpr int kExpertTile = 8;        // pairs of one expert that a CTA of the grouped product takes
+constexpr int kTensorTile = 128;      // rows of a tile of the tcgen05 grouped product (csrc/gemm_tc.cu)
 constexpr int kMaxExperts = 1024;
 
 __device__ __forceinline__ float sigmoid_of(float z) { return 1.0f / (1.0f + expf(-z)); }
@@ -305,183 +307,6 @@ moe_grouped_kernel(const T* __restrict__ x, long long ldx, const int* __restrict
   }
 }
 
-// ---- the grouped products on tensor cores (bf16) -------------------------------------------------------------------
-constexpr int kMmaTile = 64;          // pairs of one expert per CTA
-constexpr int kTensorTile = 128;      // rows of a tile of the tcgen05 grouped product (csrc/gemm_tc.cu)
-constexpr int kMmaStep = 32;          // inputs per stage
-constexpr int kMmaLd = kMmaStep + 8;  // row stride in shared memory: 80 bytes, so that ldmatrix meets no bank twice
-constexpr int kMmaStages = 3;         // a ring of three stages: two loads are in flight while one is multiplied
-
-__device__ __forceinline__ void mma_ldmatrix_x4(unsigned (&r)[4], const void* p) {
-  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-__device__ __forceinline__ void mma_ldmatrix_x2(unsigned (&r)[2], const void* p) {
-  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-__device__ __forceinline__ void mma_copy16(void* dst, const void* src) {
-  const unsigned target = (unsigned)__cvta_generic_to_shared(dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(src) : "memory");
-}
-
-// grid (tile slots, ceil(N / TILE_N)), 32 * WARPS_M * WARPS_N threads.  A CTA takes up to TILE_M sorted pairs of one
-// expert and TILE_N outputs (GATED: TILE_N gate rows and the TILE_N up rows beside them); its warps form a WARPS_M x
-// WARPS_N grid over the tile.  One shape is built: 64 x 64 with 2 x 2 warps of 32 x 32 (128 x 128 with 2 x 4 warps of
-// 64 x 32 each was measured too: 752 against 552 us for the gate and up products of 12,288 pairs over 64 experts,
-// where an expert's 192 pairs fill one and a half such tiles).  K is a multiple of 8.  Rows and results as in moe_grouped_kernel.  Dynamic shared memory:
-// kMmaStages x (TILE_M + weight rows) x kMmaLd bf16, then TILE_M ints.
-template <bool GATED, typename TO, int TILE_M, int TILE_N, int WARPS_M, int WARPS_N>
-__global__ void __launch_bounds__(32 * WARPS_M * WARPS_N)
-moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ gather, int gather_div,
-                       const __nv_bfloat16* __restrict__ w_a, const __nv_bfloat16* __restrict__ w_b, TO* __restrict__ out,
-                       long long ldo, const int* __restrict__ scatter, const int* __restrict__ tiles,
-                       const int* __restrict__ tile_count, const int* __restrict__ offsets, int K, int N) {
-  constexpr int THREADS = 32 * WARPS_M * WARPS_N;
-  constexpr int WEIGHT_ROWS = GATED ? 2 * TILE_N : TILE_N;
-  constexpr int MT = TILE_M / WARPS_M / 16;                      // 16-row tiles per warp
-  constexpr int NT = TILE_N / WARPS_N / 8;                       // 8-column tiles per warp
-  extern __shared__ __align__(16) unsigned char grouped_shared[];
-  typedef __nv_bfloat16 (*Rows)[kMmaLd];
-  Rows a_s = reinterpret_cast<Rows>(grouped_shared);                                   // [stage * TILE_M + row]
-  Rows b_s = reinterpret_cast<Rows>(grouped_shared) + kMmaStages * TILE_M;             // [stage * WEIGHT_ROWS + row]
-  int* source = reinterpret_cast<int*>(grouped_shared + (size_t)kMmaStages * (TILE_M + WEIGHT_ROWS) * kMmaLd * 2);
-  grid_launch_dependents();
-  grid_dependency_wait();
-  if ((int)blockIdx.x >= tile_count[0]) return;
-  const int thread = threadIdx.x, lane = thread & 31, warp = thread >> 5;
-  const int warp_m = warp % WARPS_M, warp_n = warp / WARPS_M;
-  const int expert = tiles[2 * blockIdx.x], start = tiles[2 * blockIdx.x + 1];
-  const int count = min(TILE_M, offsets[expert + 1] - start);
-  const int first_output = blockIdx.y * TILE_N;
-  for (int r = thread; r < TILE_M; r += THREADS)
-    source[r] = r < count ? (gather != nullptr ? gather[start + r] / gather_div : start + r) : -1;
-  __syncthreads();
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  auto stage_in = [&](int stage, int k0) {
-    for (int index = thread; index < TILE_M * 4; index += THREADS) {
-      const int r = index >> 2, c = (index & 3) * 8;
-      __nv_bfloat16* dst = &a_s[stage * TILE_M + r][c];
-      if (source[r] >= 0 && k0 + c < K) mma_copy16(dst, x + (size_t)source[r] * ldx + k0 + c);
-      else *reinterpret_cast<uint4*>(dst) = zero;
-    }
-    for (int index = thread; index < WEIGHT_ROWS * 4; index += THREADS) {
-      const int r = index >> 2, c = (index & 3) * 8;
-      const int o = first_output + (r % TILE_N);
-      const __nv_bfloat16* w = (GATED && r >= TILE_N) ? w_b : w_a;
-      __nv_bfloat16* dst = &b_s[stage * WEIGHT_ROWS + r][c];
-      if (o < N && k0 + c < K) mma_copy16(dst, w + ((size_t)expert * N + o) * K + k0 + c);
-      else *reinterpret_cast<uint4*>(dst) = zero;
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  float acc_a[MT][NT][4], acc_b[GATED ? MT : 1][NT][4];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        acc_a[mt][nt][e] = 0.0f;
-        if (GATED) acc_b[mt][nt][e] = 0.0f;
-      }
-  stage_in(0, 0);
-  if (kMmaStep < K) stage_in(1, kMmaStep);
-  int stage = 0;
-  const int row0 = warp_m * MT * 16, column0 = warp_n * NT * 8;
-  for (int k0 = 0; k0 < K; k0 += kMmaStep, stage = (stage + 1) % kMmaStages) {
-    // the stage after next is the one that was multiplied last: every warp is past it (the barrier below)
-    if (k0 + 2 * kMmaStep < K) {
-      stage_in((stage + 2) % kMmaStages, k0 + 2 * kMmaStep);
-      asm volatile("cp.async.wait_group 2;" ::: "memory");
-    } else if (k0 + kMmaStep < K) {
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-#pragma unroll
-    for (int ks = 0; ks < kMmaStep; ks += 16) {
-      unsigned a[MT][4];
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-        mma_ldmatrix_x4(a[mt], &a_s[stage * TILE_M + row0 + mt * 16 + (lane & 15)][ks + (lane >> 4) * 8]);
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        unsigned b[2];
-        mma_ldmatrix_x2(b, &b_s[stage * WEIGHT_ROWS + column0 + nt * 8 + (lane & 7)][ks + ((lane >> 3) & 1) * 8]);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) mma_bf16(acc_a[mt][nt], a[mt], b);
-        if (GATED) {
-          mma_ldmatrix_x2(b, &b_s[stage * WEIGHT_ROWS + TILE_N + column0 + nt * 8 + (lane & 7)][ks + ((lane >> 3) & 1) * 8]);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma_bf16(acc_b[mt][nt], a[mt], b);
-        }
-      }
-    }
-    __syncthreads();                                             // the stage is free for the load two steps on
-  }
-  const int g = lane >> 2, c2 = (lane & 3) * 2;
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int r = row0 + mt * 16 + g + half * 8;
-      if (r >= count) continue;
-      const int to = scatter != nullptr ? scatter[start + r] : start + r;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int o = first_output + column0 + nt * 8 + c2 + e;
-          if (o >= N) continue;
-          const float a = acc_a[mt][nt][half * 2 + e];
-          const float value = GATED ? a / (1.0f + expf(-a)) * acc_b[mt][nt][half * 2 + e] : a;
-          out[(size_t)to * ldo + o] = from_float<TO>(value);
-        }
-      }
-    }
-  }
-}
-
-template <bool GATED, typename TO, int TILE_M, int TILE_N, int WARPS_M, int WARPS_N>
-int launch_grouped_mma_as(cudaStream_t stream, const void* x, long long ldx, const int* gather, int gather_div,
-                          const void* w_a, const void* w_b, void* out, long long ldo, const int* scatter, const int* tiles,
-                          const int* tile_count, const int* offsets, int pairs, int experts, int K, int N) {
-  constexpr size_t smem = (size_t)kMmaStages * (TILE_M + (GATED ? 2 : 1) * TILE_N) * kMmaLd * 2 + TILE_M * sizeof(int);
-  static bool raised = false;
-  if (smem > 48 * 1024 && !raised) {
-    const cudaError_t err = cudaFuncSetAttribute(moe_grouped_mma_kernel<GATED, TO, TILE_M, TILE_N, WARPS_M, WARPS_N>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) {
-      mir_set_error("moe_grouped: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
-      return MIR_CUDA_ERROR;
-    }
-    raised = true;
-  }
-  const int slots = pairs / TILE_M + experts;
-  const dim3 grid(slots, (N + TILE_N - 1) / TILE_N);
-  return mir_launch(GATED ? "moe_grouped_mma_gate_up" : "moe_grouped_mma_down",
-                    moe_grouped_mma_kernel<GATED, TO, TILE_M, TILE_N, WARPS_M, WARPS_N>, grid, dim3(32 * WARPS_M * WARPS_N),
-                    smem, stream, 0, (const __nv_bfloat16*)x, ldx, gather, gather_div, (const __nv_bfloat16*)w_a,
-                    (const __nv_bfloat16*)w_b, (TO*)out, ldo, scatter, tiles, tile_count, offsets, K, N);
-}
-
-template <bool GATED, typename TO>
-int launch_grouped_mma(cudaStream_t stream, int tile_pairs, const void* x, long long ldx, const int* gather,
-                       int gather_div, const void* w_a, const void* w_b, void* out, long long ldo, const int* scatter,
-                       const int* tiles, const int* tile_count, const int* offsets, int pairs, int experts, int K, int N) {
-  (void)tile_pairs;
-  return launch_grouped_mma_as<GATED, TO, 64, 64, 2, 2>(stream, x, ldx, gather, gather_div, w_a, w_b, out, ldo, scatter,
-                                                        tiles, tile_count, offsets, pairs, experts, K, N);
-}
-
 // One CTA per token: residual[t] += sum_s weights[t, s] * pair_rows[t * top + s] (+ shared_gate[t] * shared_rows[t], or
 // + shared_rows[t] without a gate), slots in their own order.
 __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ pair_rows,
@@ -536,13 +361,13 @@ MIR_EXPORT int mir_moe_route(const float* logits, long long ld, const float* cor
 // ints for each).
 MIR_EXPORT int mir_moe_tile_slots(int pairs, int experts, int tile_pairs) { return pairs / tile_pairs + experts; }
 
-// tile_pairs: 8 for the 32-bit grouped products, 64 for the mma.sync ones, 128 for the tcgen05 ones.
+// tile_pairs: 8 for the 32-bit grouped products of this file, 128 for the tcgen05 product (csrc/gemm_tc.cu).
 // counts, first_tile: scratch of `experts` ints each.
 MIR_EXPORT int mir_moe_sort(const int* ids, int pairs, int experts, int tile_pairs, int* order, int* offsets, int* tiles,
                             int* tile_count, int* counts, int* first_tile, cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
   if (pairs < 0 || experts <= 0 || experts > kMaxExperts ||
-      (tile_pairs != kExpertTile && tile_pairs != kMmaTile && tile_pairs != kTensorTile)) {
+      (tile_pairs != kExpertTile && tile_pairs != kTensorTile)) {
     mir_set_error("moe_sort: bad sizes (pairs %d, experts %d, tiles of %d)", pairs, experts, tile_pairs);
     return MIR_BAD_ARGUMENT;
   }
@@ -562,11 +387,7 @@ MIR_EXPORT int mir_moe_gate_up(int bf16, const void* h, long long ld, const int*
                                const int* offsets, int pairs, int experts, int width, int inter, int tile_pairs,
                                cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
-  if (tile_pairs == kMmaTile) {
-    if (!bf16 || width % 8 || ld % 8) { mir_set_error("moe_gate_up: tiles of 64 pairs need bfloat16 rows of 16-byte pieces"); return MIR_BAD_ARGUMENT; }
-    return launch_grouped_mma<true, __nv_bfloat16>(stream, tile_pairs, h, ld, order, top, w_gate, w_up, hidden, inter,
-                                                   nullptr, tiles, tile_count, offsets, pairs, experts, width, inter);
-  }
+  if (tile_pairs != kExpertTile) { mir_set_error("moe_gate_up: this kernel works on tiles of %d pairs", kExpertTile); return MIR_BAD_ARGUMENT; }
   if (bf16)
     return launch_grouped<__nv_bfloat16, __nv_bfloat16, true>(stream, h, ld, order, top, w_gate, w_up, hidden, inter,
                                                               nullptr, tiles, tile_count, offsets, pairs, experts, width,
@@ -580,11 +401,7 @@ MIR_EXPORT int mir_moe_down(int bf16, const void* hidden, const int* order, cons
                             const int* tiles, const int* tile_count, const int* offsets, int pairs, int experts,
                             int width, int inter, int tile_pairs, cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
-  if (tile_pairs == kMmaTile) {
-    if (!bf16 || inter % 8) { mir_set_error("moe_down: tiles of 64 pairs need bfloat16 rows of 16-byte pieces"); return MIR_BAD_ARGUMENT; }
-    return launch_grouped_mma<false, float>(stream, tile_pairs, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows, width,
-                                            order, tiles, tile_count, offsets, pairs, experts, inter, width);
-  }
+  if (tile_pairs != kExpertTile) { mir_set_error("moe_down: this kernel works on tiles of %d pairs", kExpertTile); return MIR_BAD_ARGUMENT; }
   if (bf16)
     return launch_grouped<__nv_bfloat16, float, false>(stream, hidden, inter, nullptr, 1, w_down, nullptr, pair_rows,
                                                        width, order, tiles, tile_count, offsets, pairs, experts, inter,

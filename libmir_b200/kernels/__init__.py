@@ -786,23 +786,17 @@ class ExpertOrder:
 EXPERT_TENSOR_CORES = True       # False: the grouped products of routed experts always run as 32-bit multiply-adds
 
 
-EXPERT_TCGEN05_MIN_PAIRS = 48    # pairs per expert (on average) from which the grouped products run on tcgen05
-
-
-def expert_tile_pairs(dtype: torch.dtype, width: int, inter: int, pairs: int = 0, experts: int = 1) -> int:
-    """The tile the grouped products of routed experts work on.  bfloat16 rows of 16-byte pieces run on tensor cores:
-    tiles of 128 pairs through the tcgen05 product (TMA, accumulators in tensor memory) where an expert gets
-    EXPERT_TCGEN05_MIN_PAIRS pairs or more on average, else tiles of 64 pairs through the mma.sync kernel that streams
-    each expert's weights once; everything else runs tiles of 8 pairs with 32-bit multiply-adds."""
-    if not (EXPERT_TENSOR_CORES and dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0):
-        return 8
-    many = EXPERT_TCGEN05_MIN_PAIRS > 0 and pairs >= max(128, EXPERT_TCGEN05_MIN_PAIRS * max(1, experts))
-    return 128 if many else 64
+def expert_tile_pairs(dtype: torch.dtype, width: int, inter: int) -> int:
+    """The tile the grouped products of routed experts work on.  bfloat16 rows of 16-byte pieces: tiles of 128 pairs
+    through the tcgen05 product (TMA, accumulators in tensor memory; it beats a kernel that streams an expert's weights
+    for a tile of few pairs at every size measured, 49 against 82 us at 8 tokens).  Everything else: tiles of 8 pairs
+    with 32-bit multiply-adds."""
+    return 128 if (EXPERT_TENSOR_CORES and dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0) else 8
 
 
 def moe_sort(ids: torch.Tensor, experts: int, alloc, tile_pairs: int = 8) -> ExpertOrder:
     """Order the pairs of ids [tokens, top] by expert (a pair's place among its expert's pairs follows its index) and
-    cut each expert's run into tiles of tile_pairs (8, 64 or 128) pairs."""
+    cut each expert's run into tiles of tile_pairs (8 or 128) pairs."""
     _cuda(ids)
     _require(ids.dtype == torch.int32 and ids.is_contiguous(), "moe_sort: contiguous int32 ids are needed")
     found = ExpertOrder(alloc, ids.numel(), experts, tile_pairs)

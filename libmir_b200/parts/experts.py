@@ -11,8 +11,8 @@ With h the feed-forward's input, E experts of which each token uses `top`:
         + sigmoid(w_sg . h) * shared(h)            one number per token gates the shared expert, if there is one
 Everything runs on the device without a count ever being read back (csrc/moe.cu): the (token, expert) pairs are
 ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights (in bfloat16 on
-tensor cores: the tcgen05 product of csrc/gemm_tc.cu on tiles from a list on the device where experts get many pairs,
-an mma.sync kernel that streams each expert's weights once where they get few; in float32 as 32-bit multiply-adds), and one kernel adds the weighted rows, and the shared
+tensor cores: the tcgen05 product of csrc/gemm_tc.cu on row tiles from a list on the device; in float32 as 32-bit
+multiply-adds), and one kernel adds the weighted rows, and the shared
 expert's, into the 32-bit residual.
 """
 
@@ -93,8 +93,7 @@ class RoutedExperts(FeedForward):
         kernels.linear(x, self.router, logits, alloc=ctx.alloc)       # 32-bit accumulation and result
         kernels.moe_route(logits, self.correction, self.shared_gate, ids, weights, gate, s.experts, s.top, s.groups,
                           s.keep_groups, s.scale)
-        found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size, tokens * s.top,
-                                                                                    s.experts))
+        found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size))
         hidden = ctx.alloc((tokens * s.top, s.expert_size), dtype)
         kernels.moe_gate_up(x, found, s.top, self.w_gate, self.w_up, hidden, ctx.alloc)
         pair_rows = ctx.alloc((tokens * s.top, s.hidden_size), torch.float32)

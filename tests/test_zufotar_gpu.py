@@ -436,8 +436,8 @@ def test_router_against_the_plain_one(dtype, experts, top, groups, keep):
                                                             (33, 5, 1, 600, 24), (9, 40, 2, 24, 7), (300, 3, 2, 72, 136),
                                                             (700, 5, 3, 264, 200)])
 def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, experts, top, width, inter):
-    """Sorting by expert, the two grouped products (32-bit multiply-adds on tiles of 8 pairs, or tensor cores on
-    tiles of 64 where the sizes allow) and the weighted sum: experts without any token, experts with more pairs than
+    """Sorting by expert, the two grouped products (32-bit multiply-adds on tiles of 8 pairs, or the tcgen05 product
+    on tiles of 128 where the sizes allow) and the weighted sum: experts without any token, experts with more pairs than
     a tile, a shared expert with and without gate."""
     from libmir_b200 import kernels
     generator = torch.Generator().manual_seed(10)
@@ -450,9 +450,8 @@ def test_experts_on_ordered_pairs_against_token_by_token(dtype, tol, tokens, exp
         ids[ids == 1] = 0                                                    # expert 1 gets no token
     weights = torch.rand(tokens, top, generator=generator)
     alloc = lambda shape, kind: torch.empty(shape, dtype=kind, device=device())
-    tile = kernels.expert_tile_pairs(dtype, width, inter, tokens * top, experts)
-    on_tensor_cores = dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0
-    assert tile == ((128 if tokens * top >= max(128, 48 * experts) else 64) if on_tensor_cores else 8)
+    tile = kernels.expert_tile_pairs(dtype, width, inter)
+    assert tile == (128 if dtype == torch.bfloat16 and width % 8 == 0 and inter % 8 == 0 else 8)
     found = kernels.moe_sort(on_device(ids), experts, alloc, tile)
     order, offsets = found.order.cpu().tolist(), found.offsets.cpu().tolist()
     flat = ids.reshape(-1).tolist()

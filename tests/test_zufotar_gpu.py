@@ -682,6 +682,37 @@ def test_greedy_generation_through_the_scheduler(tmp_path, name, graphs):
         assert model.runner._graphs is not None and len(model.runner._graphs.graphs) > 0
 
 
+def test_decode_steps_replayed_from_captured_graphs_in_bfloat16(tmp_path):
+    """Two requests decoded together through captured graphs in bfloat16 (the tensor-core attention kernel with its
+    keys split, the experts on the tcgen05 product with its tiles read from the device): the teacher-forced logits of
+    every step against the plain implementation."""
+    from libmir_b200 import StepEntry, kernels
+    from libmir_b200.sampling import RequestSampler
+    config = ALL["A"]
+    folder = make_folder(tmp_path, config, seed=8, dtype="bfloat16")
+    rng = np.random.default_rng(5)
+    requests = {"a": random_ids(rng, config["vocab"], 60), "b": random_ids(rng, config["vocab"], 47)}
+    want = {name: reference(folder, ids) for name, ids in requests.items()}
+    prompt = {"a": 21, "b": 8}
+    model = load(folder, "bfloat16", 8, 40, graphs=True)
+    got = {name: [] for name in requests}
+    for name, ids in requests.items():
+        model.admit(name)
+        result = model.step([StepEntry(name, ids[:prompt[name]], range(prompt[name]))])
+        got[name].append(result.logits.float().cpu().numpy().copy())
+    for step in range(39):
+        entries = [StepEntry(name, [ids[prompt[name] + step]], [0]) for name, ids in requests.items()]
+        result = model.step(entries, [RequestSampler() for _ in entries])
+        logits = result.logits.float().cpu().numpy()
+        for row, name in enumerate(requests):
+            got[name].append(logits[row:row + 1].copy())
+    assert model.runner._graphs is not None and len(model.runner._graphs.graphs) > 0
+    everything = np.concatenate([np.concatenate(got[name]) for name in requests])
+    wanted = np.concatenate([want[name][:prompt[name] + 39] for name in requests])
+    close_logits(everything, wanted, "bfloat16", "decode steps from captured graphs")
+    assert kernels.tensor_core_linear_error() == 0
+
+
 def test_trace_runner_picks_the_design_by_its_configuration(tmp_path):
     """bin/trace_run as a user runs it: the model class comes from config.json; prompts in portions, decoded tokens,
     a pool that holds less than all requests together."""
@@ -691,17 +722,18 @@ def test_trace_runner_picks_the_design_by_its_configuration(tmp_path):
     rng = np.random.default_rng(3)
     requests = {f"q{i}": random_ids(rng, config["vocab"], n) for i, n in enumerate((100, 64, 37))}
     want = {name: reference(folder, ids) for name, ids in requests.items()}
-    for dtype in ("bfloat16", "float32"):
+    # (the third run replays every single-token step from a captured graph, as generation does)
+    for dtype, extra in (("bfloat16", []), ("float32", []), ("bfloat16", ["--decode-graphs"])):
         trace = Trace()
         for name, ids in requests.items():
             trace.step([(name, ids[:len(ids) - 10], [0, len(ids) - 11])])
             for position in range(len(ids) - 10, len(ids)):
                 trace.step([(name, ids[position:position + 1], [0])], end=[name] if position == len(ids) - 1 else [])
-        results = run_trace(folder, dtype, trace, tmp_path / f"out-{dtype}", max_tokens=128,
-                            extra_args=["--page-size", "8"])
+        results = run_trace(folder, dtype, trace, tmp_path / f"out-{dtype}-{len(extra)}", max_tokens=128,
+                            extra_args=["--page-size", "8"] + extra)
         got = np.stack([results[index][row] for index, rows in enumerate(trace.expect) for row in range(len(rows))])
         wanted = np.stack([want[name][position] for rows in trace.expect for name, position in rows])
-        close_logits(got, wanted, dtype, f"trace {dtype}")
+        close_logits(got, wanted, dtype, f"trace {dtype} {extra}")
 
 
 def test_generate_command_line(tmp_path):

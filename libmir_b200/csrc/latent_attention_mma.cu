@@ -11,6 +11,7 @@
 // The key tile is read from the pages once per 64 query rows, which for decoded tokens means once for all heads.
 // With more than one partition a CTA walks over its share of the keys only and leaves an unnormalised partial result
 // (sum, maximum, weights' sum per row); a second kernel merges them.  Scores, softmax and sums are 32-bit.
+#include <algorithm>
 #include <cfloat>
 #include "common.cuh"
 #include "launchers.h"
@@ -62,13 +63,13 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
                         const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ query_starts, const int* __restrict__ context_lens, int page_size,
                         int heads, int width, int rank, float scale, int partition_keys, int partitions,
-                        float* __restrict__ partial_o, float* __restrict__ partial_ml) {
+                        float* __restrict__ partial_o, float* __restrict__ partial_ml, int query_rows, int key_buffers) {
   extern __shared__ __align__(16) unsigned char shared[];
   const int padded = (width + 15) / 16 * 16;                    // the reduction runs in steps of 16
   const int ld = padded + 8;                                     // row stride of the query and key tiles (elements)
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(shared);
-  __nv_bfloat16* k_s = q_s + (size_t)kRows * ld;
-  float* s_s = reinterpret_cast<float*>(k_s + (size_t)kKeys * ld);
+  __nv_bfloat16* k_s = q_s + (size_t)query_rows * ld;            // query_rows: what the launch keeps of the 64 (a multiple of 16)
+  float* s_s = reinterpret_cast<float*>(k_s + (size_t)key_buffers * kKeys * ld);   // key_buffers: 1, or 2 where they fit
   constexpr int lds = kKeys + 4;
   __nv_bfloat16* p_s = reinterpret_cast<__nv_bfloat16*>(s_s + kRows * lds);
   constexpr int ldp = kKeys + 8;
@@ -90,16 +91,19 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
   const int key_begin = blockIdx.z * partition_keys;
   const int key_end = min(min((blockIdx.z + 1) * partition_keys, last_position + 1), context);
   const int* table = block_table + (size_t)row * table_width;
-  const int chunks = padded / 8;                                 // 16-byte pieces per tile row
 
-  // the query rows of this block
-  for (int index = thread; index < kRows * chunks; index += kThreads) {
-    const int r = index / chunks, c = index - r * chunks;
+  // the query rows of this block: four threads copy a row, 16 bytes at a time (no division in the loop)
+  {
+    const int r = thread >> 2;
     const int pair = first_pair + r;
-    uint4 value = make_uint4(0u, 0u, 0u, 0u);
-    if (pair < pairs && c * 8 < width)
-      value = *reinterpret_cast<const uint4*>(q + (size_t)(start + pair / heads) * q_stride + (size_t)(pair % heads) * width + c * 8);
-    *reinterpret_cast<uint4*>(q_s + (size_t)r * ld + c * 8) = value;
+    const bool there = pair < pairs;
+    const __nv_bfloat16* from = there ? q + (size_t)(start + pair / heads) * q_stride + (size_t)(pair % heads) * width : q;
+    __nv_bfloat16* to = q_s + (size_t)r * ld;
+    for (int c = (thread & 3) * 8; c < padded && r < query_rows; c += 32) {
+      uint4 value = make_uint4(0u, 0u, 0u, 0u);
+      if (there && c < width) value = *reinterpret_cast<const uint4*>(from + c);
+      *reinterpret_cast<uint4*>(to + c) = value;
+    }
   }
 
   // softmax owners: 4 threads per query row
@@ -119,20 +123,34 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
   const int first_column = warp * NT * 8;
   const int row_tiles = (min(kRows, pairs - first_pair) + 15) / 16;   // tiles of 16 query rows that hold any row
 
+  // four threads copy a key's row: one look at the block table per thread and tile, then 16-byte copies
+  auto fetch_keys = [&](int k0, __nv_bfloat16* tile) {
+    const int r = thread >> 2;
+    const int key = k0 + r;
+    const int page = key < key_end ? table[key / page_size] : -1;
+    const __nv_bfloat16* from = page >= 0 ? pages + ((size_t)page * page_size + key % page_size) * width : pages;
+    __nv_bfloat16* to = tile + (size_t)r * ld;
+    for (int c = (thread & 3) * 8; c < padded; c += 32) {
+      if (page >= 0 && c < width) copy16(to + c, from + c);
+      else *reinterpret_cast<uint4*>(to + c) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  __nv_bfloat16* const first_tile = k_s;
+  int buffer = 0;
   for (int k0 = key_begin; k0 < key_end; k0 += kKeys) {
-    __syncthreads();                                             // the tile before is done with (and q_s is written)
-    for (int index = thread; index < kKeys * chunks; index += kThreads) {
-      const int r = index / chunks, c = index - r * chunks;
-      const int key = k0 + r;
-      __nv_bfloat16* dst = k_s + (size_t)r * ld + c * 8;
-      const int page = key < key_end ? table[key / page_size] : -1;
-      if (page >= 0 && c * 8 < width)
-        copy16(dst, pages + ((size_t)page * page_size + key % page_size) * width + c * 8);
-      else
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    // One buffer: the tile is fetched here, after everybody is done with the tile before.  Two buffers: this tile was
+    // asked for while the tile before was multiplied, and the next one is asked for as soon as this one has landed.
+    if (key_buffers == 1 || k0 == key_begin) {
+      __syncthreads();                                           // (also: q_s is written)
+      fetch_keys(k0, first_tile + (size_t)buffer * kKeys * ld);
     }
     copy_wait_all();
     __syncthreads();
+    k_s = first_tile + (size_t)buffer * kKeys * ld;
+    if (key_buffers == 2) {
+      if (k0 + kKeys < key_end) fetch_keys(k0 + kKeys, first_tile + (size_t)(buffer ^ 1) * kKeys * ld);
+      buffer ^= 1;
+    }
     // S = Q K^T: this warp's 8 keys against all 64 query rows
     {
       float s[4][4];
@@ -301,17 +319,18 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ partial_
   }
 }
 
-size_t shared_bytes(int width) {
+size_t shared_bytes(int width, int query_rows = kRows, int key_buffers = 1) {
   const int padded = (width + 15) / 16 * 16;
   const size_t ld = padded + 8;
-  return (size_t)(kRows + kKeys) * ld * 2 + (size_t)kRows * (kKeys + 4) * 4 + (size_t)kRows * (kKeys + 8) * 2 + 3 * kRows * 4;
+  return (size_t)(query_rows + key_buffers * kKeys) * ld * 2 + (size_t)kRows * (kKeys + 4) * 4 +
+         (size_t)kRows * (kKeys + 8) * 2 + 3 * kRows * 4;
 }
 
 template <int NT>
 int launch(cudaStream_t stream, dim3 grid, size_t smem, const void* q, long long q_stride, void* out, const void* pages,
            const int* block_table, int table_width, const int* query_starts, const int* context_lens, int page_size,
            int heads, int width, int rank, float scale, int partition_keys, int partitions, float* partial_o,
-           float* partial_ml) {
+           float* partial_ml, int query_rows, int key_buffers) {
   static size_t raised = 0;
   if (smem > raised) {
     const cudaError_t err = cudaFuncSetAttribute(latent_attention_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -324,7 +343,8 @@ int launch(cudaStream_t stream, dim3 grid, size_t smem, const void* q, long long
   }
   latent_attention_kernel<NT><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, block_table, table_width,
-      query_starts, context_lens, page_size, heads, width, rank, scale, partition_keys, partitions, partial_o, partial_ml);
+      query_starts, context_lens, page_size, heads, width, rank, scale, partition_keys, partitions, partial_o, partial_ml,
+      query_rows, key_buffers);
   return mir_check_launch("latent_attention");
 }
 
@@ -353,12 +373,15 @@ MIR_EXPORT int mir_latent_attention_bf16(const void* q, long long q_stride, void
     return MIR_BAD_ARGUMENT;
   }
   const dim3 grid((max_pairs + kRows - 1) / kRows, num_rows, partitions);
-  const size_t smem = shared_bytes(width);
+  // decoded tokens bring few query rows: the shared memory they leave holds a second key tile, fetched during the products
+  const int query_rows = std::min(kRows, (max_pairs + 15) / 16 * 16);
+  const int key_buffers = shared_bytes(width, query_rows, 2) <= 227 * 1024 ? 2 : 1;
+  const size_t smem = shared_bytes(width, query_rows, key_buffers);
   int status;
 #define MIR_LATENT(N)                                                                                              \
   status = launch<N>(stream, grid, smem, q, q_stride, out, pages, block_table, table_width, query_starts,         \
                      context_lens, page_size, heads, width, rank, scale, partition_keys, partitions, partial_o, \
-                     partial_ml)
+                     partial_ml, query_rows, key_buffers)
   if (rank <= 64) MIR_LATENT(1);
   else if (rank <= 128) MIR_LATENT(2);
   else if (rank <= 256) MIR_LATENT(4);

@@ -66,7 +66,7 @@ constexpr int kLanes = 8;                                        // lanes that s
 // channels 4 (m kLanes + l) .. + 3, m < PER / 4.  The inputs of kScanChunk tokens at a time are staged in shared
 // memory (every column of a head reads the same r, k and decay); the read-out's sum over the lanes is no part of the
 // chain from state to state.  One lane count and one order of sums for every shape of step.
-template <typename T, int PER>
+template <typename T, int PER, bool SHORT>
 __global__ void __launch_bounds__(kScanWarps * 32)
 wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, long long ld,
                 const float* __restrict__ decay_raw, const float* __restrict__ decay_bias, const float* __restrict__ bonus,
@@ -76,7 +76,8 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   constexpr int BLOCK_COLUMNS = COLUMNS * kScanWarps;
   constexpr int PADDED = kLanes * PER;
   constexpr int ROW = 3 * PADDED + 4 + BLOCK_COLUMNS;            // r | k | decay | bonus term | v of this CTA's columns
-  constexpr int kScanChunk = PER <= 8 ? kScanChunkNarrow : (PER <= 16 ? kScanChunkWide : kScanChunkWidest);
+  // SHORT: a step of single tokens stages one token a warp: few registers, so that all its CTAs are resident at once
+  constexpr int kScanChunk = SHORT ? kScanWarps : (PER <= 8 ? kScanChunkNarrow : (PER <= 16 ? kScanChunkWide : kScanChunkWidest));
   __shared__ __align__(16) float staged[kScanChunk * ROW];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -114,7 +115,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   // every column of the head.
   constexpr int TOKENS_PER_WARP = kScanChunk / kScanWarps;
   constexpr int PER_LANE = PADDED / 32;
-  constexpr int VALUES_PER_THREAD = kScanChunk * BLOCK_COLUMNS / (kScanWarps * 32);
+  constexpr int VALUES_PER_THREAD = (kScanChunk * BLOCK_COLUMNS + kScanWarps * 32 - 1) / (kScanWarps * 32);
   float next_r[TOKENS_PER_WARP][PER_LANE], next_k[TOKENS_PER_WARP][PER_LANE], next_w[TOKENS_PER_WARP][PER_LANE];
   float next_v[VALUES_PER_THREAD];
   auto fetch = [&](int from) {
@@ -139,6 +140,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
       const int index = thread + j * kScanWarps * 32;
       const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
       next_v[j] = (t < count && first_column + c < dim) ? to_float(v[(size_t)(from + t) * ld + head_at + first_column + c]) : 0.0f;
+      // (t may lie beyond the chunk where the chunk has fewer values than the CTA has threads: commit skips those)
     }
   };
   auto commit = [&](int from) {
@@ -166,7 +168,7 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     for (int j = 0; j < VALUES_PER_THREAD; ++j) {
       const int index = thread + j * kScanWarps * 32;
       const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
-      staged[t * ROW + 3 * PADDED + 4 + c] = next_v[j];
+      if (t < kScanChunk) staged[t * ROW + 3 * PADDED + 4 + c] = next_v[j];
     }
   };
   fetch(start);
@@ -218,12 +220,12 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   }
 }
 
-template <typename T, int PER>
+template <typename T, int PER, bool SHORT>
 int launch_scan(cudaStream_t stream, const void* r, const void* k, const void* v, long long ld, const float* decay_raw,
                 const float* decay_bias, const float* bonus, float* state, const int* query_starts,
                 const int* state_slots, const int* positions, float* out, int rows, int heads, int dim) {
   constexpr int columns = kScanWarps * (32 / kLanes);
-  return mir_launch("wkv_scan", wkv_scan_kernel<T, PER>, dim3(rows, heads, (dim + columns - 1) / columns),
+  return mir_launch("wkv_scan", wkv_scan_kernel<T, PER, SHORT>, dim3(rows, heads, (dim + columns - 1) / columns),
                     dim3(32, kScanWarps), 0, stream, 0, (const T*)r, (const T*)k, (const T*)v, ld, decay_raw, decay_bias,
                     bonus, state, query_starts, state_slots, positions, out, heads, dim);
 }
@@ -232,10 +234,13 @@ template <typename T>
 int launch_scan_for(cudaStream_t stream, const void* r, const void* k, const void* v, long long ld,
                     const float* decay_raw, const float* decay_bias, const float* bonus, float* state,
                     const int* query_starts, const int* state_slots, const int* positions, float* out, int rows,
-                    int heads, int dim) {
-#define MIR_WKV(P)                                                                                                 \
-  return launch_scan<T, P>(stream, r, k, v, ld, decay_raw, decay_bias, bonus, state, query_starts, state_slots, \
-                           positions, out, rows, heads, dim);
+                    int heads, int dim, bool single_tokens) {
+#define MIR_WKV(P)                                                                                                  \
+  if (single_tokens)                                                                                                \
+    return launch_scan<T, P, true>(stream, r, k, v, ld, decay_raw, decay_bias, bonus, state, query_starts,         \
+                                   state_slots, positions, out, rows, heads, dim);                                 \
+  return launch_scan<T, P, false>(stream, r, k, v, ld, decay_raw, decay_bias, bonus, state, query_starts,          \
+                                  state_slots, positions, out, rows, heads, dim);
   if (dim <= 32) { MIR_WKV(4) }
   if (dim <= 64) { MIR_WKV(8) }
   if (dim <= 96) { MIR_WKV(12) }
@@ -287,9 +292,10 @@ MIR_EXPORT int mir_wkv_scan(int bf16, const void* r, const void* k, const void* 
     mir_set_error("wkv_scan: bad sizes (tokens %d, rows %d, heads %d, dim %d)", tokens, rows, heads, dim);
     return MIR_BAD_ARGUMENT;
   }
+  const bool single_tokens = tokens == rows;                     // a step of decoded tokens: every row brings one
   if (bf16)
     return launch_scan_for<__nv_bfloat16>(stream, r, k, v, ld, decay_raw, decay_bias, bonus, state, query_starts,
-                                          state_slots, positions, out, rows, heads, dim);
+                                          state_slots, positions, out, rows, heads, dim, single_tokens);
   return launch_scan_for<float>(stream, r, k, v, ld, decay_raw, decay_bias, bonus, state, query_starts, state_slots,
-                                positions, out, rows, heads, dim);
+                                positions, out, rows, heads, dim, single_tokens);
 }
